@@ -1,0 +1,188 @@
+// Torch registration: torch.classes.flashoverlap_class.{OverlapImpl,BaselineImpl} and
+// torch.ops.flashoverlap_op.*, with the reference's method names and argument orders
+// (src/pybind.cpp:114-150) plus the additions this library makes (marked below).
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <c10/cuda/CUDAStream.h>
+#include <torch/custom_class.h>
+#include <torch/library.h>
+
+#include "comm/nccl_utils.h"
+#include "flags/fo_wait.h"
+#include "norm/fo_norm.h"
+#include "runtime/baseline_impl.h"
+#include "runtime/fused_common.h"
+#include "runtime/loopback.h"
+#include "runtime/overlap_impl.h"
+
+namespace {
+
+using fo::BaselineImpl;
+using fo::OverlapImpl;
+
+int sm_count_of_current_device() {
+  return at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+}
+
+bool is_bf16(const at::Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda() && t.is_contiguous(), name, " must be a contiguous CUDA tensor");
+  TORCH_CHECK(t.scalar_type() == at::kBFloat16 || t.scalar_type() == at::kHalf, name,
+              " must be bfloat16 or float16");
+  return t.scalar_type() == at::kBFloat16;
+}
+
+std::vector<int64_t> generate_nccl_id() { return fo::generate_nccl_id(); }
+
+// X: tile-contiguous [rows*dim]; RX: row-major output [rows, dim]; RW: [dim].
+void reorder_rmsnorm_eps(at::Tensor X, at::Tensor RX, at::Tensor RW, int64_t BM, int64_t BN,
+                         int64_t rldn, at::Tensor RA, double eps) {
+  const bool bf = is_bf16(X, "X");
+  TORCH_CHECK(RX.scalar_type() == X.scalar_type() && RW.scalar_type() == X.scalar_type(),
+              "X, RX and RW must share a dtype");
+  TORCH_CHECK(RX.dim() == 2 && RX.is_contiguous() && RX.is_cuda(), "RX must be [rows, dim]");
+  const int rows = static_cast<int>(RX.size(0));
+  const int dim = static_cast<int>(RX.size(1));
+  TORCH_CHECK(X.numel() >= RX.numel() && RW.numel() == dim, "shape mismatch");
+  TORCH_CHECK(RA.is_cuda() && RA.scalar_type() == at::kInt && RA.is_contiguous() &&
+                  RA.numel() >= static_cast<int64_t>(rows / BM) * (dim / BN),
+              "RA must be an int32 CUDA tensor with one entry per tile");
+  c10::cuda::CUDAGuard guard(X.device());
+  fo::cuda_check(fo::reorder_rmsnorm_launch(X.data_ptr(), RX.data_ptr(), RW.data_ptr(), rows, dim,
+                                            static_cast<int>(BM), static_cast<int>(BN),
+                                            static_cast<int>(rldn), RA.data_ptr<int>(),
+                                            static_cast<float>(eps), bf, sm_count_of_current_device(),
+                                            c10::cuda::getCurrentCUDAStream().stream()),
+                 "reorder_rmsnorm");
+}
+
+// Reference signature (src/pybind.cpp:149): eps fixed at 1e-5 as in src/rmsnorm/rmsnorm.cuh:102.
+void reorder_rmsnorm(at::Tensor X, at::Tensor RX, at::Tensor RW, int64_t BM, int64_t BN,
+                     int64_t rldn, at::Tensor RA) {
+  reorder_rmsnorm_eps(X, RX, RW, BM, BN, rldn, RA, 1e-5);
+}
+
+void rmsnorm(at::Tensor X, at::Tensor RX, at::Tensor RW, double eps) {
+  const bool bf = is_bf16(X, "X");
+  TORCH_CHECK(RX.scalar_type() == X.scalar_type() && RW.scalar_type() == X.scalar_type(),
+              "X, RX and RW must share a dtype");
+  TORCH_CHECK(X.dim() == 2 && RX.sizes() == X.sizes() && RX.is_contiguous() && RX.is_cuda(),
+              "X and RX must be [rows, dim]");
+  const int rows = static_cast<int>(X.size(0));
+  const int dim = static_cast<int>(X.size(1));
+  TORCH_CHECK(RW.numel() == dim, "RW must have dim elements");
+  c10::cuda::CUDAGuard guard(X.device());
+  fo::cuda_check(fo::rmsnorm_launch(X.data_ptr(), RX.data_ptr(), RW.data_ptr(), rows, dim,
+                                    static_cast<float>(eps), bf, sm_count_of_current_device(),
+                                    c10::cuda::getCurrentCUDAStream().stream()),
+                 "rmsnorm");
+}
+
+void reorder_impl(at::Tensor X, at::Tensor Y, int64_t rows, int64_t dim, int64_t BM, int64_t BN,
+                  int64_t rldn, at::Tensor RA, bool to_reordered) {
+  is_bf16(X, "X");
+  TORCH_CHECK(Y.scalar_type() == X.scalar_type() && Y.is_cuda() && Y.is_contiguous(),
+              "Y must match X's dtype");
+  TORCH_CHECK(X.numel() == rows * dim && Y.numel() == rows * dim, "X and Y must hold rows*dim elements");
+  TORCH_CHECK(RA.is_cuda() && RA.scalar_type() == at::kInt && RA.is_contiguous() &&
+                  RA.numel() >= (rows / BM) * (dim / BN),
+              "RA must be an int32 CUDA tensor with one entry per tile");
+  c10::cuda::CUDAGuard guard(X.device());
+  fo::cuda_check(fo::reorder_launch(X.data_ptr(), Y.data_ptr(), static_cast<int>(rows),
+                                    static_cast<int>(dim), static_cast<int>(BM), static_cast<int>(BN),
+                                    static_cast<int>(rldn), RA.data_ptr<int>(), to_reordered,
+                                    sm_count_of_current_device(),
+                                    c10::cuda::getCurrentCUDAStream().stream()),
+                 "reorder");
+}
+
+// Y (tile-contiguous) <- X (row-major [rows, dim]).
+void reorder(at::Tensor X, at::Tensor Y, int64_t BM, int64_t BN, int64_t rldn, at::Tensor RA) {
+  TORCH_CHECK(X.dim() == 2, "X must be [rows, dim]");
+  reorder_impl(X, Y, X.size(0), X.size(1), BM, BN, rldn, RA, true);
+}
+
+// Y (row-major [rows, dim]) <- X (tile-contiguous).
+void unreorder(at::Tensor X, at::Tensor Y, int64_t BM, int64_t BN, int64_t rldn, at::Tensor RA) {
+  TORCH_CHECK(Y.dim() == 2, "Y must be [rows, dim]");
+  reorder_impl(X, Y, Y.size(0), Y.size(1), BM, BN, rldn, RA, false);
+}
+
+// Bounded counting wait on MM[index] (see flags/fo_wait.h); status: int32[8] CUDA tensor.
+void wait_flag(int64_t target, at::Tensor MM, int64_t index, int64_t timeout_ms, at::Tensor status) {
+  TORCH_CHECK(MM.is_cuda() && MM.scalar_type() == at::kInt && MM.is_contiguous() &&
+                  index >= 0 && index < MM.numel(),
+              "MM must be an int32 CUDA tensor and index in range");
+  TORCH_CHECK(status.is_cuda() && status.scalar_type() == at::kInt &&
+                  status.numel() >= fo::kStatusWords,
+              "status must be an int32 CUDA tensor with 8 words");
+  c10::cuda::CUDAGuard guard(MM.device());
+  fo::cuda_check(fo::wait_flag_launch(static_cast<int>(target), MM.data_ptr<int>() + index,
+                                      static_cast<int>(index),
+                                      static_cast<uint64_t>(timeout_ms) * 1000000ull,
+                                      status.data_ptr<int>(),
+                                      c10::cuda::getCurrentCUDAStream().stream()),
+                 "wait_flag");
+}
+
+// Flattened Algo table: for each Algo index (BM, BN, BK, stages, raster strip width).
+std::vector<int64_t> algo_table() {
+  std::vector<int64_t> t;
+  for (int a = 0; a < fo::kNumAlgos; ++a) {
+    const fo::AlgoConfig c = fo::algo_config(a);
+    t.insert(t.end(), {c.bm, c.bn, c.bk, c.stages, c.raster_sw});
+  }
+  return t;
+}
+
+}  // namespace
+
+TORCH_LIBRARY(flashoverlap_class, m) {
+  m.class_<BaselineImpl>("BaselineImpl")
+      .def(torch::init())
+      .def("nccl_init", &BaselineImpl::NcclInit)
+      .def("cublas_init", &BaselineImpl::CublasInit)
+      .def("gemm_allreduce", &BaselineImpl::GemmAllReduce)
+      .def("gemm_reducescatter", &BaselineImpl::GemmReduceScatter)
+      .def("gemm_all2all", &BaselineImpl::GemmAll2All)
+      .def("cublas_gemm", &BaselineImpl::Gemm)
+      .def("nccl_allreduce", &BaselineImpl::NcclAllReduce)
+      .def("nccl_reducescatter", &BaselineImpl::NcclReduceScatter)
+      .def("nccl_all2all", &BaselineImpl::NcclAll2All);
+  m.class_<OverlapImpl>("OverlapImpl")
+      .def(torch::init())
+      .def("cutlass_init", &OverlapImpl::CutlassInit)
+      .def("cutlass_gemm", &OverlapImpl::Gemm)
+      .def("gemm_allreduce_overlap", &OverlapImpl::GemmAllReduceOverlap)
+      .def("gemm_reducescatter_overlap", &OverlapImpl::GemmReduceScatterOverlap)
+      .def("nccl_init", &OverlapImpl::NcclInit)
+      .def("gemm_allreduce", &OverlapImpl::GemmAllReduce)
+      .def("gemm_reducescatter", &OverlapImpl::GemmReduceScatter)
+      .def("gemm_all2all", &OverlapImpl::GemmAll2All)
+      .def("overlap_init", &OverlapImpl::OverlapInit)
+      .def("nccl_allreduce", &OverlapImpl::NcclAllReduce)
+      .def("nccl_reducescatter", &OverlapImpl::NcclReduceScatter)
+      .def("nccl_all2all", &OverlapImpl::NcclAll2All)
+      .def("seg_allreduce", &OverlapImpl::SegAllReduce)
+      // additions
+      .def("gemm_allreduce_fused", &OverlapImpl::GemmAllReduceFused)
+      .def("gemm_reducescatter_fused", &OverlapImpl::GemmReduceScatterFused)
+      .def("set_option", &OverlapImpl::SetOption)
+      .def("get_option", &OverlapImpl::GetOption)
+      .def("symm_empty", &OverlapImpl::SymmEmpty)
+      .def("read_status", &OverlapImpl::ReadStatus)
+      .def("check_status", &OverlapImpl::CheckStatus)
+      .def("reset_status", &OverlapImpl::ResetStatus);
+}
+
+TORCH_LIBRARY(flashoverlap_op, m) {
+  m.def("generate_nccl_id", &generate_nccl_id);
+  m.def("reorder_rmsnorm", &reorder_rmsnorm);
+  // additions
+  m.def("reorder_rmsnorm_eps", &reorder_rmsnorm_eps);
+  m.def("rmsnorm", &rmsnorm);
+  m.def("reorder", &reorder);
+  m.def("unreorder", &unreorder);
+  m.def("wait_flag", &wait_flag);
+  m.def("algo_table", &algo_table);
+  m.def("fused_loopback", &fo::fused_loopback);
+}

@@ -1,0 +1,94 @@
+// Host/device-shared parameter block of the tcgen05 GEMM family and the table of tile
+// configurations ("Algo" indices) that the JSON configs and the tuner refer to.
+// The reference indexes 102 CUTLASS instantiations by an integer Algo
+// (src/tiling/gemm_dispatcher.h:7-27, tool/generate_instances.py:5-45); here an Algo names a
+// (BN, pipeline depth, raster strip width) triple of one hand-written kernel.
+#pragma once
+#include <cuda.h>
+#include <cstdint>
+
+namespace fo {
+
+constexpr int kBM = 128;  // tile rows = UMMA M (one TMEM lane per row)
+constexpr int kBK = 64;   // 64 x 16-bit = one 128-byte swizzle atom along K
+constexpr int kMaxRanks = 8;
+constexpr int kMaxVirtualRanks = 4;
+
+enum OutMode : int {
+  kOutNatural = 0,      // row-major [M, N]
+  kOutReorder = 1,      // tile-contiguous, tile t at position RA[t] (reference layout)
+  kOutScatterRows = 2,  // reorder + per-row remap through RE (reduce-scatter staging layout)
+};
+
+enum CommMode : int {
+  kCommNone = 0,
+  kCommFusedAR = 2,
+  kCommFusedRS = 3,
+};
+
+// One tensor map per virtual rank.  A launch normally carries one rank (gridDim.y == 1);
+// the single-GPU emulation used by the tests runs several ranks' CTAs in one cooperative
+// launch, each rank with its own operands.
+struct GemmTensorMaps {
+  CUtensorMap a[kMaxVirtualRanks];
+  CUtensorMap b[kMaxVirtualRanks];
+};
+
+struct GemmParams {
+  int M, N, K;
+  int tiles_m, tiles_n, num_tiles;
+  int raster_sw;     // strip width (in N tiles) of the tile sweep
+  int out_mode;      // OutMode
+  int rldn;          // reordered layout: tiles per reordered row (reference rLDN, 1 in practice)
+  int signal;        // bump MM[group] after each tile (counter-gated NCCL path)
+  int monitor;       // record per-tile completion order in MM rows 1..TM
+  int mm_stride;     // row length of MM (= tiles_n in the reference's callers)
+  int num_groups;    // entries of cseg; 0 => one group per tile
+  int comm;          // CommMode
+  int ws;            // ranks taking part in the fused collective
+  int rank_base;     // rank of virtual rank 0 of this launch
+  int strided_rows;  // 1: row i of a tile belongs to rank i % ws (reference), 0: contiguous
+  uint32_t epoch_done_prev;  // value `done` must have reached before the first push
+  uint32_t epoch_done;       // value `done` reaches when this call is complete everywhere
+  uint64_t timeout_ns;       // bound for every cross-GPU wait
+  const int* RA;             // [num_tiles] natural tile id -> reordered position (nullptr: identity)
+  const int* RE;             // [M*N/BN] row remap for kOutScatterRows
+  const int* cseg;           // [num_groups] tiles per group (device)
+  // indexed by virtual rank
+  void* out[kMaxVirtualRanks];          // plain/signalling output
+  int* MM[kMaxVirtualRanks];            // counters / monitor matrix
+  int32_t* status[kMaxVirtualRanks];    // status words
+  uint32_t* local_cnt[kMaxVirtualRanks];  // CTAs of this rank that finished reducing
+  // indexed by rank (peer-mapped addresses valid on the launching GPU)
+  void* stage[kMaxRanks];      // staging: [src rank][tile][rows owned][BN]
+  uint32_t* flags[kMaxRanks];  // per tile / per group arrival counters
+  uint32_t* done[kMaxRanks];   // per-call completion counter
+  void* dst[kMaxRanks];        // AllReduce: every rank's output; ReduceScatter: dst[rank] only
+};
+
+// ------------------------------------------------------------------ Algo table
+
+struct AlgoConfig {
+  int bm, bn, bk;
+  int stages;
+  int raster_sw;  // 0 => full row panels (strip = all N tiles)
+};
+
+constexpr int kNumAlgos = 24;
+
+inline AlgoConfig algo_config(int algo) {
+  // algo = raster index * 4 + kernel index
+  static const int kKernelBN[4] = {256, 256, 128, 128};
+  static const int kKernelStages[4] = {4, 3, 6, 4};
+  static const int kRaster[6] = {8, 4, 2, 1, 16, 0};
+  if (algo < 0 || algo >= kNumAlgos) algo = 0;
+  AlgoConfig c;
+  c.bm = kBM;
+  c.bk = kBK;
+  c.bn = kKernelBN[algo & 3];
+  c.stages = kKernelStages[algo & 3];
+  c.raster_sw = kRaster[algo >> 2];
+  return c;
+}
+
+}  // namespace fo

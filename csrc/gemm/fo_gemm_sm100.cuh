@@ -1,0 +1,542 @@
+// Persistent, warp-specialised tcgen05 GEMM for B200 (sm_100a) with three kinds of epilogue:
+//
+//   * plain      C = A * B^T written row-major, tile-contiguous ("reordered") or row-scattered;
+//   * signalling the same plus a per-wave-group counter bump (and an optional completion-order
+//                monitor) once a tile is globally visible - the producer half of the
+//                counter-gated NCCL path the reference is built around
+//                (reference: src/overlap/gemm_with_signal.h:210-256, :338-361);
+//   * fused      the tile's bf16/fp16 partial sums are pushed, row slice by row slice, straight
+//                into the owning peer GPU's staging buffer over NVLink, the owner's reducer
+//                warps (in the same kernel) sum the `ws` partials in fp32 as soon as every
+//                rank's slice has landed, and write the result to every rank's output
+//                (AllReduce) or to the local shard (ReduceScatter).  This replaces the
+//                reference's GEMM + wait kernel + NCCL call (src/overlap_impl.cu:214-321).
+//
+// Roles inside a CTA (one CTA per SM, 128 x BN output tiles, BK = 64):
+//   warp 0      TMA producer: 2-D tiled loads (128-byte swizzle, no multicast) into a
+//               STAGES-deep shared-memory ring, completion counted on mbarriers;
+//   warp 1      MMA issuer: one thread issues tcgen05.mma.kind::f16 (fp32 accumulate in TMEM),
+//               tcgen05.commit releases ring slots and publishes finished accumulators;
+//               this warp also owns the TMEM allocation (2 accumulators of BN columns);
+//   warps 2-5   epilogue: tcgen05.ld -> convert -> swizzled shared-memory transpose ->
+//               128-byte coalesced global (local or peer) stores, then the signal;
+//   warps 6-9   (fused only) reducer for the row slices this rank owns.
+// The two TMEM accumulators let tile i's epilogue run under tile i+1's main loop.
+//
+// Every wait is bounded: on expiry the role records a status code, raises a CTA-wide abort
+// flag, the producer drains its TMA loads in flight, TMEM is freed and the kernel returns.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <cstdint>
+
+#include "../common/fo_ptx.cuh"
+#include "fo_gemm_params.h"
+
+namespace fo {
+
+template <int BN, int STAGES>
+struct GemmSmem {
+  static constexpr int kABytes = kBM * kBK * 2;
+  static constexpr int kBBytes = BN * kBK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kEpiBufBytes = kBM * 128;  // 128 rows x 64 16-bit columns
+  static constexpr int kRingBytes = STAGES * kStageBytes;
+  static constexpr int kEpiOffset = kRingBytes;
+  static constexpr int kBarOffset = kEpiOffset + 2 * kEpiBufBytes;
+  static constexpr int kNumBars = 2 * STAGES + 4;
+  static constexpr int kMiscOffset = kBarOffset + kNumBars * 8;
+  static constexpr int kMiscBytes = 64;
+  // +1024: the ring is aligned up to 1024 B at run time (128-byte swizzle atom).
+  static constexpr int kTotalBytes = kMiscOffset + kMiscBytes + 1024;
+};
+
+struct TileCoord {
+  int m, n;
+};
+
+// Position in the launch order -> tile coordinates.  Tiles are swept in column strips
+// `sw` tiles wide, M-major inside a strip; sw == tiles_n gives row-panel-major order.
+__device__ __forceinline__ TileCoord tile_of_position(int pos, int tiles_m, int tiles_n, int sw) {
+  const int per_strip = tiles_m * sw;
+  const int s = pos / per_strip;
+  const int q = pos - s * per_strip;
+  const int w = min(sw, tiles_n - s * sw);
+  TileCoord c;
+  c.m = q / w;
+  c.n = s * sw + (q - c.m * w);
+  return c;
+}
+
+// Wave group of reordered position r: groups are runs of cseg[g] consecutive positions.
+__device__ __forceinline__ void group_of_position(const GemmParams& p, int r, int* g, int* need) {
+  if (p.num_groups <= 0 || p.cseg == nullptr) {
+    *g = r;
+    *need = 1;
+    return;
+  }
+  int acc = 0, i = 0, n = 1;
+  for (; i < p.num_groups; ++i) {
+    n = p.cseg[i];
+    acc += n;
+    if (r < acc) break;
+  }
+  if (i >= p.num_groups) i = p.num_groups - 1;
+  *g = i;
+  *need = n;
+}
+
+template <bool BF16>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  if constexpr (BF16) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  } else {
+    __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+}
+
+template <bool BF16>
+__device__ __forceinline__ void unpack_add(uint32_t w, float& lo, float& hi) {
+  if constexpr (BF16) {
+    __nv_bfloat162 v = *reinterpret_cast<__nv_bfloat162*>(&w);
+    float2 f = __bfloat1622float2(v);
+    lo += f.x;
+    hi += f.y;
+  } else {
+    __half2 v = *reinterpret_cast<__half2*>(&w);
+    float2 f = __half22float2(v);
+    lo += f.x;
+    hi += f.y;
+  }
+}
+
+constexpr int kEpilogueThreads = 128;
+constexpr int kReducerThreads = 128;
+constexpr int kThreadsPlain = 64 + kEpilogueThreads;
+constexpr int kThreadsFused = kThreadsPlain + kReducerThreads;
+
+template <int BN, int STAGES, bool BF16, bool FUSED>
+__global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
+    fo_gemm_kernel(const __grid_constant__ GemmTensorMaps maps,
+                   const __grid_constant__ GemmParams p) {
+  using L = GemmSmem<BN, STAGES>;
+  extern __shared__ uint8_t smem_raw[];
+  // The ring must start on a 1024-byte boundary of the shared window.
+  const uint32_t raw_addr = ptx::smem_u32(smem_raw);
+  uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
+
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOffset);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + STAGES;
+  uint64_t* tmem_full_bar = bars + 2 * STAGES;
+  uint64_t* tmem_empty_bar = bars + 2 * STAGES + 2;
+  uint32_t* misc = reinterpret_cast<uint32_t*>(smem + L::kMiscOffset);
+  uint32_t* s_tmem_base = misc;                                   // written by tcgen05.alloc
+  volatile int* s_abort = reinterpret_cast<volatile int*>(misc + 1);
+  volatile int* s_ep_ok = reinterpret_cast<volatile int*>(misc + 2);
+  volatile int* s_is_last = reinterpret_cast<volatile int*>(misc + 3);
+  // two slots, alternated per tile: a slow reader of tile i never sees tile i+1's verdict
+  volatile int* s_red_ok = reinterpret_cast<volatile int*>(misc + 4);
+
+  const int warp_idx = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int vr = blockIdx.y;           // virtual rank of this CTA inside the launch
+  const int me = p.rank_base + vr;     // rank this CTA acts as
+  const int num_kb = (p.K + kBK - 1) / kBK;
+  constexpr uint32_t kTmemCols = 2 * BN;
+  int32_t* status = p.status[vr];
+  // Pipeline waits inside the CTA can legitimately last as long as a cross-GPU wait that
+  // another role is sitting in, so their bound is a multiple of it.
+  const uint64_t pipe_timeout = 4ull * p.timeout_ns + 1000000000ull;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < STAGES; ++i) {
+      ptx::mbar_init(&full_bar[i], 1);
+      ptx::mbar_init(&empty_bar[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      ptx::mbar_init(&tmem_full_bar[i], 1);
+      ptx::mbar_init(&tmem_empty_bar[i], kEpilogueThreads);
+    }
+    *s_abort = 0;
+    *s_ep_ok = 1;
+    s_red_ok[0] = 1;
+    s_red_ok[1] = 1;
+    *s_is_last = 0;
+    ptx::mbar_fence_init();
+  }
+  if (warp_idx == 0 && lane == 0) {
+    ptx::prefetch_tmap(&maps.a[vr]);
+    ptx::prefetch_tmap(&maps.b[vr]);
+  }
+  if (warp_idx == 1) {
+    ptx::tmem_alloc(s_tmem_base, kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem_base = *s_tmem_base;
+
+  if (warp_idx == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      uint32_t issued = 0;
+      bool ok = true;
+      for (int pos = blockIdx.x; ok && pos < p.num_tiles; pos += gridDim.x) {
+        const TileCoord tc = tile_of_position(pos, p.tiles_m, p.tiles_n, p.raster_sw);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!ptx::mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, s_abort, pipe_timeout)) {
+            ptx::report_status(status, kStatusTimeoutSmemEmpty, pos, kb, stage);
+            *s_abort = 1;
+            ok = false;
+            break;
+          }
+          uint8_t* sa = smem + stage * L::kStageBytes;
+          uint8_t* sb = sa + L::kABytes;
+          ptx::mbar_arrive_expect_tx(&full_bar[stage], L::kStageBytes);
+          ptx::tma_load_2d(sa, &maps.a[vr], &full_bar[stage], kb * kBK, tc.m * kBM);
+          ptx::tma_load_2d(sb, &maps.b[vr], &full_bar[stage], kb * kBK, tc.n * BN);
+          ++issued;
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+      // Drain: do not leave the CTA while a bulk copy may still write its shared memory.
+      // For each ring slot wait (bounded) for the last load issued into it.
+      for (int s = 0; s < STAGES; ++s) {
+        if (issued <= static_cast<uint32_t>(s)) continue;
+        const uint32_t last = ((issued - 1 - s) / STAGES) * STAGES + s;  // last issue index on slot s
+        const uint32_t par = (last / STAGES) & 1u;
+        for (uint32_t it = 0; it < ptx::kMbarDrainPolls; ++it) {
+          if (ptx::mbar_try_wait(&full_bar[s], par)) break;
+        }
+      }
+    }
+  } else if (warp_idx == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = ptx::make_idesc_f16(BF16, kBM, BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int pos = blockIdx.x; ok && pos < p.num_tiles; pos += gridDim.x) {
+        if (!ptx::mbar_wait_bounded(&tmem_empty_bar[acc], acc_phase ^ 1u, s_abort, pipe_timeout)) {
+          ptx::report_status(status, kStatusTimeoutTmemEmpty, pos, acc, 0);
+          *s_abort = 1;
+          break;
+        }
+        ptx::tc_fence_after_sync();
+        const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(acc * BN);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!ptx::mbar_wait_bounded(&full_bar[stage], phase, s_abort, pipe_timeout)) {
+            ptx::report_status(status, kStatusTimeoutSmemFull, pos, kb, stage);
+            *s_abort = 1;
+            ok = false;
+            break;
+          }
+          ptx::tc_fence_after_sync();
+          const uint32_t sa = ptx::smem_u32(smem + stage * L::kStageBytes);
+          const uint64_t da = ptx::make_smem_desc_sw128_kmajor(sa);
+          const uint64_t db = ptx::make_smem_desc_sw128_kmajor(sa + L::kABytes);
+#pragma unroll
+          for (int k = 0; k < kBK / 16; ++k) {
+            // advance 16 elements (32 B) along K inside the swizzle atom: +2 in 16-byte units
+            ptx::umma_f16_ss(tmem_d, da + static_cast<uint64_t>(2 * k),
+                             db + static_cast<uint64_t>(2 * k), idesc,
+                             (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          ptx::umma_commit(&empty_bar[stage]);  // slot reusable once these MMAs have read it
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+        ptx::umma_commit(&tmem_full_bar[acc]);  // accumulator complete
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
+      }
+    }
+  } else if (warp_idx < 6) {
+    // ------------------------------------------------------------------ epilogue
+    const int et = threadIdx.x - 64;           // 0..127
+    const int quad = warp_idx & 3;             // TMEM lane quadrant this warp may read
+    const int my_row = quad * 32 + lane;       // tile row held by this thread after tcgen05.ld
+    uint8_t* epi = smem + L::kEpiOffset;
+    const int rows_owned = kBM / p.ws;
+    const size_t elem = 2;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool first_push = true;
+
+    for (int pos = blockIdx.x; pos < p.num_tiles; pos += gridDim.x) {
+      const TileCoord tc = tile_of_position(pos, p.tiles_m, p.tiles_n, p.raster_sw);
+      const int t = tc.m * p.tiles_n + tc.n;
+      const int r = (p.RA != nullptr) ? p.RA[t] : t;
+
+      if (et == 0) {
+        int ok = ptx::mbar_wait_bounded(&tmem_full_bar[acc], acc_phase, s_abort, pipe_timeout) ? 1 : 0;
+        if (!ok) {
+          ptx::report_status(status, kStatusTimeoutTmemFull, pos, acc, 0);
+          *s_abort = 1;
+        }
+        if (FUSED && ok && first_push) {
+          // Peers may still be reading the staging slices of the previous call.
+          uint32_t obs;
+          if (!ptx::wait_counter_ge<true>(p.done[me], p.epoch_done_prev, p.timeout_ns, s_abort,
+                                          &obs)) {
+            ptx::report_status(status, kStatusTimeoutStartFlag, me, obs, p.epoch_done_prev);
+            *s_abort = 1;
+            ok = 0;
+          }
+        }
+        *s_ep_ok = ok;
+      }
+      first_push = false;
+      ptx::named_bar_sync(1, kEpilogueThreads);
+      if (!*s_ep_ok) break;
+      ptx::tc_fence_after_sync();
+
+      // Per-thread destinations for the cooperative store phase: thread `et` stores the
+      // 16-byte piece (et & 7) of rows (et >> 3) + 16 * i, i = 0..7.
+      uint8_t* row_ptr[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int lr = (et >> 3) + 16 * i;
+        size_t off;  // element offset of (row lr, tile column 0)
+        uint8_t* base;
+        if constexpr (FUSED) {
+          const int o = p.strided_rows ? (lr % p.ws) : (lr / rows_owned);
+          const int q = p.strided_rows ? (lr / p.ws) : (lr % rows_owned);
+          base = reinterpret_cast<uint8_t*>(p.stage[o]);
+          off = ((static_cast<size_t>(me) * p.num_tiles + t) * rows_owned + q) * BN;
+        } else {
+          base = reinterpret_cast<uint8_t*>(p.out[vr]);
+          if (p.out_mode == kOutNatural) {
+            off = (static_cast<size_t>(tc.m) * kBM + lr) * p.N + static_cast<size_t>(tc.n) * BN;
+          } else if (p.out_mode == kOutReorder) {
+            const size_t ld = static_cast<size_t>(p.rldn) * BN;
+            off = static_cast<size_t>(r / p.rldn) * kBM * ld + static_cast<size_t>(r % p.rldn) * BN +
+                  static_cast<size_t>(lr) * ld;
+          } else {  // kOutScatterRows: rows of the [M*N/BN, BN] view are remapped through RE
+            const size_t row_id = static_cast<size_t>(r) * kBM + lr;
+            off = static_cast<size_t>(p.RE[row_id]) * BN;
+          }
+        }
+        row_ptr[i] = base + off * elem + (et & 7) * 16;
+      }
+
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) +
+                             static_cast<uint32_t>(acc * BN);
+#pragma unroll 1
+      for (int c = 0; c < BN / 64; ++c) {
+        uint32_t v0[32], v1[32];
+        ptx::tmem_ld_32x32b_x32(t_row + c * 64, v0);
+        ptx::tmem_ld_32x32b_x32(t_row + c * 64 + 32, v1);
+        ptx::tmem_ld_wait();
+        if (c == BN / 64 - 1) {
+          // Accumulator fully read: hand it back to the MMA warp.
+          ptx::tc_fence_before_sync();
+          ptx::mbar_arrive(&tmem_empty_bar[acc]);
+        }
+        uint8_t* buf = epi + (c & 1) * L::kEpiBufBytes + my_row * 128;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint4 w;
+          w.x = pack2<BF16>(__uint_as_float(v0[8 * j + 0]), __uint_as_float(v0[8 * j + 1]));
+          w.y = pack2<BF16>(__uint_as_float(v0[8 * j + 2]), __uint_as_float(v0[8 * j + 3]));
+          w.z = pack2<BF16>(__uint_as_float(v0[8 * j + 4]), __uint_as_float(v0[8 * j + 5]));
+          w.w = pack2<BF16>(__uint_as_float(v0[8 * j + 6]), __uint_as_float(v0[8 * j + 7]));
+          *reinterpret_cast<uint4*>(buf + ((j ^ (my_row & 7)) * 16)) = w;
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint4 w;
+          w.x = pack2<BF16>(__uint_as_float(v1[8 * j + 0]), __uint_as_float(v1[8 * j + 1]));
+          w.y = pack2<BF16>(__uint_as_float(v1[8 * j + 2]), __uint_as_float(v1[8 * j + 3]));
+          w.z = pack2<BF16>(__uint_as_float(v1[8 * j + 4]), __uint_as_float(v1[8 * j + 5]));
+          w.w = pack2<BF16>(__uint_as_float(v1[8 * j + 6]), __uint_as_float(v1[8 * j + 7]));
+          *reinterpret_cast<uint4*>(buf + (((j + 4) ^ (my_row & 7)) * 16)) = w;
+        }
+        ptx::named_bar_sync(1, kEpilogueThreads);
+        const uint8_t* rbuf = epi + (c & 1) * L::kEpiBufBytes;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int lr = (et >> 3) + 16 * i;
+          const uint4 w =
+              *reinterpret_cast<const uint4*>(rbuf + lr * 128 + (((et & 7) ^ (lr & 7)) * 16));
+          ptx::st_v4(row_ptr[i] + c * 128, w);
+        }
+      }
+
+      // All of this tile's stores have been issued by every epilogue thread.
+      ptx::named_bar_sync(1, kEpilogueThreads);
+      if constexpr (FUSED) {
+        if (et < p.ws) {
+          int g, need;
+          group_of_position(p, r, &g, &need);
+          ptx::fence_acq_rel_sys();
+          ptx::red_release_sys_add(p.flags[et] + g, 1u);
+        }
+      } else {
+        if (et == 0 && p.MM[vr] != nullptr) {
+          int* mm = p.MM[vr];
+          if (p.signal) {
+            int g, need;
+            group_of_position(p, r, &g, &need);
+            ptx::fence_acq_rel_gpu();
+            ptx::red_release_gpu_add(reinterpret_cast<uint32_t*>(mm + g), 1u);
+          }
+          if (p.monitor) {
+            const int order = atomicAdd(mm + p.mm_stride - 1, 1);
+            mm[p.mm_stride + r] = order;
+          }
+        }
+      }
+      if (FUSED && et == 0 && p.monitor && p.MM[vr] != nullptr) {
+        int* mm = p.MM[vr];
+        const int order = atomicAdd(mm + p.mm_stride - 1, 1);
+        mm[p.mm_stride + r] = order;
+      }
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+  } else {
+    // ------------------------------------------------------------------ reducer (fused)
+    if constexpr (FUSED) {
+      const int rt = threadIdx.x - kThreadsPlain;  // 0..127
+      const int ws = p.ws;
+      const int rows_owned = kBM / ws;
+      constexpr int kVecPerRow = BN / 8;
+      const int total_vec = rows_owned * kVecPerRow;
+      const size_t src_stride = static_cast<size_t>(p.num_tiles) * rows_owned * BN;  // elements
+      const uint8_t* stage_me = reinterpret_cast<const uint8_t*>(p.stage[me]);
+
+      int slot = 0;
+      for (int pos = blockIdx.x; pos < p.num_tiles; pos += gridDim.x, slot ^= 1) {
+        const TileCoord tc = tile_of_position(pos, p.tiles_m, p.tiles_n, p.raster_sw);
+        const int t = tc.m * p.tiles_n + tc.n;
+        const int r = (p.RA != nullptr) ? p.RA[t] : t;
+        if (rt == 0) {
+          int g, need;
+          group_of_position(p, r, &g, &need);
+          uint32_t obs;
+          const uint32_t target = static_cast<uint32_t>(need * ws);
+          int ok = ptx::wait_counter_ge<true>(p.flags[me] + g, target, p.timeout_ns, s_abort, &obs)
+                       ? 1
+                       : 0;
+          if (!ok) {
+            ptx::report_status(status, kStatusTimeoutGroupFlag, g, obs, target);
+            *s_abort = 1;
+          }
+          s_red_ok[slot] = ok;
+        }
+        ptx::named_bar_sync(2, kReducerThreads);
+        if (!s_red_ok[slot]) break;
+
+        // Output addressing of this tile.
+        size_t out_base;  // element offset of (tile row 0, col 0) in the destination
+        size_t out_ld;
+        if (p.comm == kCommFusedAR) {
+          if (p.out_mode == kOutNatural) {
+            out_ld = p.N;
+            out_base = static_cast<size_t>(tc.m) * kBM * p.N + static_cast<size_t>(tc.n) * BN;
+          } else {
+            out_ld = static_cast<size_t>(p.rldn) * BN;
+            out_base = static_cast<size_t>(r / p.rldn) * kBM * out_ld +
+                       static_cast<size_t>(r % p.rldn) * BN;
+          }
+        } else {  // ReduceScatter: local shard [M/ws, N]
+          if (p.out_mode == kOutNatural) {
+            out_ld = p.N;
+            out_base = static_cast<size_t>(tc.m) * rows_owned * p.N + static_cast<size_t>(tc.n) * BN;
+          } else {  // tiles of rows_owned x BN in reordered order
+            out_ld = BN;
+            out_base = static_cast<size_t>(r) * rows_owned * BN;
+          }
+        }
+        const uint8_t* src_tile = stage_me + static_cast<size_t>(t) * rows_owned * BN * 2;
+
+        for (int v = rt; v < total_vec; v += kReducerThreads) {
+          const int q = v / kVecPerRow;
+          const int c8 = v - q * kVecPerRow;
+          float a[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) a[i] = 0.f;
+          const uint8_t* sp = src_tile + (static_cast<size_t>(q) * BN + c8 * 8) * 2;
+#pragma unroll 8
+          for (int s = 0; s < ws; ++s) {
+            const uint4 x = ptx::ld_cg_v4(sp + static_cast<size_t>(s) * src_stride * 2);
+            unpack_add<BF16>(x.x, a[0], a[1]);
+            unpack_add<BF16>(x.y, a[2], a[3]);
+            unpack_add<BF16>(x.z, a[4], a[5]);
+            unpack_add<BF16>(x.w, a[6], a[7]);
+          }
+          uint4 y;
+          y.x = pack2<BF16>(a[0], a[1]);
+          y.y = pack2<BF16>(a[2], a[3]);
+          y.z = pack2<BF16>(a[4], a[5]);
+          y.w = pack2<BF16>(a[6], a[7]);
+          if (p.comm == kCommFusedAR) {
+            const int lr = p.strided_rows ? (q * ws + me) : (me * rows_owned + q);
+            const size_t off = (out_base + static_cast<size_t>(lr) * out_ld + c8 * 8) * 2;
+            for (int d = 0; d < ws; ++d) {
+              const int dd = (me + d) % ws;  // start with the local copy, then fan out
+              ptx::st_v4(reinterpret_cast<uint8_t*>(p.dst[dd]) + off, y);
+            }
+          } else {
+            const size_t off = (out_base + static_cast<size_t>(q) * out_ld + c8 * 8) * 2;
+            ptx::st_v4(reinterpret_cast<uint8_t*>(p.dst[me]) + off, y);
+          }
+        }
+      }
+
+      // End-of-call handshake.  The last CTA of this rank to finish clears the group flags
+      // (nobody on this rank reads them any more and peers cannot push again before they
+      // have seen our `done` signal), tells every rank that this rank has consumed its
+      // staging, and - for AllReduce - waits until every rank's results have landed here.
+      ptx::named_bar_sync(2, kReducerThreads);
+      if (rt == 0) {
+        ptx::fence_acq_rel_sys();
+        const uint32_t old = atomicAdd(p.local_cnt[vr], 1u);
+        *s_is_last = (old == gridDim.x - 1) ? 1 : 0;
+      }
+      ptx::named_bar_sync(2, kReducerThreads);
+      if (*s_is_last) {
+        const int nflags = (p.num_groups > 0 && p.cseg != nullptr) ? p.num_groups : p.num_tiles;
+        for (int i = rt; i < nflags; i += kReducerThreads) p.flags[me][i] = 0u;
+        ptx::named_bar_sync(2, kReducerThreads);
+        if (rt == 0) {
+          *p.local_cnt[vr] = 0u;
+          ptx::fence_acq_rel_sys();
+          for (int d = 0; d < ws; ++d) ptx::red_release_sys_add(p.done[(me + d) % ws], 1u);
+          if (p.comm == kCommFusedAR) {
+            uint32_t obs;
+            if (!ptx::wait_counter_ge<true>(p.done[me], p.epoch_done, p.timeout_ns, nullptr,
+                                            &obs)) {
+              ptx::report_status(status, kStatusTimeoutDoneFlag, me, obs, p.epoch_done);
+            }
+          }
+        }
+      }
+    }
+  }
+
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if (warp_idx == 1) {
+    ptx::tc_fence_after_sync();
+    ptx::tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+}  // namespace fo

@@ -1,0 +1,85 @@
+// Pieces shared by the runtime classes and the single-GPU loopback driver: the layout of the
+// symmetric "signal" region, operand checks and the GemmParams set-up of one call.
+#pragma once
+#include <ATen/ATen.h>
+#include <c10/cuda/CUDAStream.h>
+#include <cuda_runtime.h>
+
+#include <string>
+
+#include "../comm/symmetric_heap.h"
+#include "../common/fo_status.h"
+#include "../gemm/fo_gemm.h"
+
+namespace fo {
+
+// Signal region layout (bytes).  `done` and `local_cnt` sit on separate 128-byte lines so
+// that remote atomics on one never contend with local atomics on the other.
+constexpr size_t kSignalDoneOffset = 0;
+constexpr size_t kSignalLocalCntOffset = 128;
+constexpr size_t kSignalFlagsOffset = 1024;
+constexpr size_t kSignalMaxFlags = 65536;
+constexpr size_t kSignalBytes = kSignalFlagsOffset + kSignalMaxFlags * sizeof(uint32_t);
+
+inline void cuda_check(cudaError_t e, const char* what) {
+  TORCH_CHECK(e == cudaSuccess, "CUDA failure in ", what, ": ", cudaGetErrorString(e));
+}
+
+struct GemmShape {
+  int M, N, K;
+  bool bf16;
+};
+
+// A [M,K], B [N,K] (weight layout), both contiguous, same 16-bit floating type.
+inline GemmShape check_operands(const at::Tensor& A, const at::Tensor& B) {
+  TORCH_CHECK(A.is_cuda() && B.is_cuda(), "A and B must be CUDA tensors");
+  TORCH_CHECK(A.dim() == 2 && B.dim() == 2, "A must be [M,K] and B must be [N,K]");
+  TORCH_CHECK(A.is_contiguous() && B.is_contiguous(), "A and B must be contiguous");
+  TORCH_CHECK(A.scalar_type() == B.scalar_type(), "A and B must have the same dtype");
+  TORCH_CHECK(A.scalar_type() == at::kBFloat16 || A.scalar_type() == at::kHalf,
+              "only bfloat16 and float16 operands are supported");
+  TORCH_CHECK(A.size(1) == B.size(1), "A [M,K] and B [N,K] disagree on K");
+  GemmShape s;
+  s.M = static_cast<int>(A.size(0));
+  s.K = static_cast<int>(A.size(1));
+  s.N = static_cast<int>(B.size(0));
+  s.bf16 = A.scalar_type() == at::kBFloat16;
+  return s;
+}
+
+inline void check_out(const at::Tensor& C, const at::Tensor& A, int64_t numel, const char* name) {
+  TORCH_CHECK(C.is_cuda() && C.is_contiguous(), name, " must be a contiguous CUDA tensor");
+  TORCH_CHECK(C.scalar_type() == A.scalar_type(), name, " must have the operands' dtype");
+  TORCH_CHECK(C.numel() >= numel, name, " is too small: needs ", numel, " elements");
+}
+
+inline const int* int_ptr_or_null(const at::Tensor& t, const char* name) {
+  if (!t.defined() || t.numel() == 0) return nullptr;
+  TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kInt && t.is_contiguous(), name,
+              " must be a contiguous int32 CUDA tensor");
+  return t.data_ptr<int>();
+}
+
+// Shape, tiling and tensor maps for virtual rank `vr` of a launch.
+inline void setup_problem(int algo, const at::Tensor& A, const at::Tensor& B, int vr,
+                          GemmTensorMaps* maps, GemmParams* p, bool* bf16) {
+  const GemmShape s = check_operands(A, B);
+  if (vr == 0) {
+    p->M = s.M;
+    p->N = s.N;
+    p->K = s.K;
+    const std::string err = prepare_tiling(algo, p);
+    TORCH_CHECK(err.empty(), err, " (M=", s.M, " N=", s.N, " K=", s.K, " Algo=", algo, ")");
+    *bf16 = s.bf16;
+  } else {
+    TORCH_CHECK(p->M == s.M && p->N == s.N && p->K == s.K && *bf16 == s.bf16,
+                "all ranks of a loopback launch must use the same shape and dtype");
+  }
+  const AlgoConfig c = algo_config(algo);
+  std::string e = encode_tmap_16bit(&maps->a[vr], A.data_ptr(), s.M, s.K, kBM);
+  TORCH_CHECK(e.empty(), "A: ", e);
+  e = encode_tmap_16bit(&maps->b[vr], B.data_ptr(), s.N, s.K, c.bn);
+  TORCH_CHECK(e.empty(), "B: ", e);
+}
+
+}  // namespace fo

@@ -1,0 +1,28 @@
+// Single-GPU emulation of the fused GEMM+collective kernels: all `ws` ranks' CTAs run in ONE
+// cooperative launch on the current device (rank = blockIdx.y), each rank with its own
+// operands, staging, flags and outputs.  The code path inside the kernel is the one the
+// multi-GPU launch uses; only the addresses in the per-rank tables differ.  This is how the
+// cross-rank protocol is tested where a single GPU is available.  (Separate launches, one
+// per rank, must never be used for this: kernels that wait on one another are not
+// guaranteed to be co-resident.)  The reference has no counterpart.
+#pragma once
+#include <ATen/ATen.h>
+
+#include <string>
+#include <vector>
+
+namespace fo {
+
+// comm_op: "all_reduce" or "reduce_scatter".  A[r] is [M,K], B[r] is [N,K]; out[r] is [M,N]
+// (all_reduce) or [M/ws,N] (reduce_scatter).  RA / cseg_gpu may be None
+// (identity order / one flag per tile).  natural_out selects row-major results instead of
+// the tile-contiguous layout.  The call is repeated `repeat` times back to back to exercise
+// the call-to-call handshake.  Returns ws * kStatusWords status words.
+std::vector<int64_t> fused_loopback(std::string comm_op, std::vector<at::Tensor> A,
+                                    std::vector<at::Tensor> B, std::vector<at::Tensor> out,
+                                    c10::optional<at::Tensor> RA,
+                                    c10::optional<at::Tensor> cseg_gpu, int64_t algo,
+                                    bool strided_rows, bool natural_out, int64_t repeat,
+                                    int64_t timeout_ms);
+
+}  // namespace fo

@@ -1,0 +1,516 @@
+#include "overlap_impl.h"
+
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <c10/cuda/CUDAStream.h>
+
+#include <algorithm>
+#include <cstring>
+
+#include "../comm/nccl_utils.h"
+#include "../flags/fo_wait.h"
+#include "fused_common.h"
+
+namespace fo {
+
+OverlapImpl::OverlapImpl() {}
+
+OverlapImpl::~OverlapImpl() {
+  // Streams and events first, then the symmetric memory, then the communicator.
+  if (comm_done_ != nullptr) cudaEventDestroy(comm_done_);
+  if (gemm_start_ != nullptr) cudaEventDestroy(gemm_start_);
+  if (comm_stream_ != nullptr) cudaStreamDestroy(comm_stream_);
+  heap_.reset();
+  if (comm_ != nullptr) ncclCommDestroy(comm_);  // the reference never destroys its communicator
+}
+
+cudaStream_t OverlapImpl::stream() const {
+  // The stream current in torch at call time.  (The reference freezes the stream that was
+  // current when cutlass_init ran, src/overlap_impl.cu:31-33; following the caller's stream
+  // context is what torch users expect, and is identical for callers on the default stream.)
+  return c10::cuda::getCurrentCUDAStream().stream();
+}
+
+ncclDataType_t OverlapImpl::nccl_dtype(const at::Tensor& t) const {
+  if (t.scalar_type() == at::kBFloat16) return ncclBfloat16;
+  if (t.scalar_type() == at::kHalf) return ncclFloat16;
+  if (t.scalar_type() == at::kFloat) return ncclFloat32;
+  TORCH_CHECK(false, "unsupported dtype for a collective");
+}
+
+void OverlapImpl::NcclInit(int64_t rank, int64_t world, std::vector<int64_t> id) {
+  TORCH_CHECK(world >= 1 && world <= kMaxRanks, "world size must be in [1, ", kMaxRanks, "]");
+  TORCH_CHECK(rank >= 0 && rank < world, "rank out of range");
+  TORCH_CHECK(comm_ == nullptr && heap_ == nullptr, "nccl_init was already called");
+  rank_ = static_cast<int>(rank);
+  world_ = static_cast<int>(world);
+  cuda_check(cudaGetDevice(&device_), "cudaGetDevice");
+  cudaDeviceProp prop;
+  cuda_check(cudaGetDeviceProperties(&prop, device_), "cudaGetDeviceProperties");
+  sm_count_ = prop.multiProcessorCount;
+  if (world_ > 1) {
+    ncclUniqueId uid = unpack_nccl_id(id);
+    FO_NCCL_CHECK(ncclCommInitRank(&comm_, world_, uid, rank_));
+  }
+  heap_ = std::make_unique<SymmetricHeap>(rank_, world_, comm_, false);
+  status_ = at::zeros({kStatusWords}, at::TensorOptions().dtype(at::kInt).device(at::kCUDA, device_));
+}
+
+void OverlapImpl::CutlassInit() {
+  if (heap_ == nullptr) NcclInit(0, 1, {});
+}
+
+void OverlapImpl::ensure_comm_stream() {
+  if (comm_stream_ != nullptr) return;
+  int lo = 0, hi = 0;
+  cuda_check(cudaDeviceGetStreamPriorityRange(&lo, &hi), "cudaDeviceGetStreamPriorityRange");
+  cuda_check(cudaStreamCreateWithPriority(&comm_stream_, cudaStreamNonBlocking, hi),
+             "cudaStreamCreateWithPriority");
+  cuda_check(cudaEventCreateWithFlags(&comm_done_, cudaEventDisableTiming), "cudaEventCreate");
+  cuda_check(cudaEventCreateWithFlags(&gemm_start_, cudaEventDisableTiming), "cudaEventCreate");
+}
+
+void OverlapImpl::OverlapInit() {
+  if (heap_ == nullptr) NcclInit(0, 1, {});
+  ensure_comm_stream();
+}
+
+void OverlapImpl::SetOption(std::string name, int64_t value) {
+  if (name == "mode") {
+    TORCH_CHECK(value == 0 || value == 1, "mode must be 0 (fused) or 1 (gated)");
+    opt_mode_ = value;
+  } else if (name == "strided_rows") {
+    opt_strided_rows_ = value ? 1 : 0;
+  } else if (name == "sm_margin") {
+    TORCH_CHECK(value >= 0 && value < sm_count_, "sm_margin out of range");
+    opt_sm_margin_ = value;
+  } else if (name == "timeout_ms") {
+    TORCH_CHECK(value > 0, "timeout_ms must be positive");
+    opt_timeout_ms_ = value;
+  } else {
+    TORCH_CHECK(false, "unknown option '", name, "'");
+  }
+}
+
+int64_t OverlapImpl::GetOption(std::string name) {
+  if (name == "mode") return opt_mode_;
+  if (name == "strided_rows") return opt_strided_rows_;
+  if (name == "sm_margin") return opt_sm_margin_;
+  if (name == "timeout_ms") return opt_timeout_ms_;
+  if (name == "sm_count") return sm_count_;
+  if (name == "rank") return rank_;
+  if (name == "world") return world_;
+  if (name == "num_algos") return kNumAlgos;
+  TORCH_CHECK(false, "unknown option '", name, "'");
+}
+
+at::Tensor OverlapImpl::SymmEmpty(std::vector<int64_t> sizes, std::string dtype) {
+  TORCH_CHECK(heap_ != nullptr, "call nccl_init first");
+  at::ScalarType st;
+  if (dtype == "bfloat16" || dtype == "bf16") {
+    st = at::kBFloat16;
+  } else if (dtype == "float16" || dtype == "fp16" || dtype == "half") {
+    st = at::kHalf;
+  } else if (dtype == "float32" || dtype == "fp32") {
+    st = at::kFloat;
+  } else {
+    TORCH_CHECK(false, "unsupported dtype '", dtype, "'");
+  }
+  int64_t numel = 1;
+  for (int64_t s : sizes) {
+    TORCH_CHECK(s >= 0, "negative size");
+    numel *= s;
+  }
+  const size_t bytes = std::max<size_t>(static_cast<size_t>(numel) * c10::elementSize(st), 256);
+  SymmetricRegion* reg = heap_->allocate(bytes, stream());
+  // The region belongs to this object; the tensor is a view and must not outlive it.
+  return at::from_blob(reg->local(), sizes, [](void*) {},
+                       at::TensorOptions().dtype(st).device(at::kCUDA, device_));
+}
+
+std::vector<int64_t> OverlapImpl::ReadStatus() {
+  TORCH_CHECK(status_.defined(), "call nccl_init first");
+  at::Tensor h = status_.cpu();
+  std::vector<int64_t> out(kStatusWords);
+  for (int i = 0; i < kStatusWords; ++i) out[i] = h.data_ptr<int>()[i];
+  return out;
+}
+
+void OverlapImpl::CheckStatus() {
+  const std::vector<int64_t> s = ReadStatus();
+  TORCH_CHECK(s[kStatusWordCode] == kStatusOk, "flashoverlap device status: ",
+              status_name(static_cast<int32_t>(s[kStatusWordCode])), " (args ", s[kStatusWordArg0],
+              ", ", s[kStatusWordArg1], ", ", s[kStatusWordArg2], ") on rank ", rank_);
+}
+
+void OverlapImpl::ResetStatus() {
+  TORCH_CHECK(status_.defined(), "call nccl_init first");
+  status_.zero_();
+  if (signal_ != nullptr) {
+    char* base = static_cast<char*>(signal_->local());
+    cuda_check(cudaMemsetAsync(base + kSignalLocalCntOffset, 0, 128, stream()), "cudaMemsetAsync");
+    cuda_check(cudaMemsetAsync(base + kSignalFlagsOffset, 0, kSignalMaxFlags * sizeof(uint32_t),
+                               stream()),
+               "cudaMemsetAsync");
+  }
+}
+
+// ---------------------------------------------------------------------------- plain GEMM
+
+void OverlapImpl::run_plain(const at::Tensor& A, const at::Tensor& B, void* out, int out_mode,
+                            const int* RA, const int* RE, int rldn, int* MM, int mm_stride,
+                            bool signal, bool monitor, const int* cseg, int num_groups, int algo,
+                            int grid_cap) {
+  if (heap_ == nullptr) NcclInit(0, 1, {});
+  c10::cuda::CUDAGuard guard(A.device());
+  GemmTensorMaps maps;
+  GemmParams p;
+  std::memset(&p, 0, sizeof(p));
+  bool bf16 = true;
+  setup_problem(algo, A, B, 0, &maps, &p, &bf16);
+  p.out_mode = out_mode;
+  p.rldn = rldn < 1 ? 1 : rldn;
+  p.signal = signal ? 1 : 0;
+  p.monitor = monitor ? 1 : 0;
+  p.mm_stride = mm_stride;
+  p.num_groups = num_groups;
+  p.comm = kCommNone;
+  p.ws = 1;
+  p.rank_base = rank_;
+  p.timeout_ns = static_cast<uint64_t>(opt_timeout_ms_) * 1000000ull;
+  p.RA = RA;
+  p.RE = RE;
+  p.cseg = cseg;
+  p.out[0] = out;
+  p.MM[0] = MM;
+  p.status[0] = status_.data_ptr<int>();
+  const int grid = std::max(1, std::min(std::min(grid_cap, sm_count_), p.num_tiles));
+  cuda_check(launch_gemm(algo, bf16, false, maps, p, grid, 1, false, stream()), "GEMM launch");
+}
+
+void OverlapImpl::Gemm(at::Tensor A, at::Tensor B, at::Tensor C, int64_t Algo) {
+  const GemmShape s = check_operands(A, B);
+  check_out(C, A, static_cast<int64_t>(s.M) * s.N, "C");
+  run_plain(A, B, C.data_ptr(), kOutNatural, nullptr, nullptr, 1, nullptr, 0, false, false, nullptr,
+            0, static_cast<int>(Algo), sm_count_);
+}
+
+// ---------------------------------------------------------------------------- bare collectives
+
+void OverlapImpl::NcclAllReduce(at::Tensor C) {
+  if (world_ == 1) return;
+  FO_NCCL_CHECK(ncclAllReduce(C.data_ptr(), C.data_ptr(), C.numel(), nccl_dtype(C), ncclSum, comm_,
+                              stream()));
+}
+
+void OverlapImpl::SegAllReduce(at::Tensor C, at::Tensor cSEG_CPU, int64_t SegNum) {
+  // Equal units of numel / SegNum elements; segment s covers cSEG_CPU[s] units
+  // (reference: src/overlap_impl.cu:153-168).
+  if (world_ == 1) return;
+  TORCH_CHECK(!cSEG_CPU.is_cuda() && cSEG_CPU.scalar_type() == at::kInt, "cSEG_CPU: int32 host tensor");
+  const int* seg = cSEG_CPU.data_ptr<int>();
+  const int64_t unit = C.numel() / SegNum;
+  char* base = static_cast<char*>(C.data_ptr());
+  const size_t es = C.element_size();
+  int64_t acc = 0;
+  int64_t units = 0;
+  for (int64_t s = 0; s < cSEG_CPU.numel() && units < SegNum; ++s) {
+    const int64_t n = unit * seg[s];
+    FO_NCCL_CHECK(ncclAllReduce(base + acc * es, base + acc * es, n, nccl_dtype(C), ncclSum, comm_,
+                                stream()));
+    acc += n;
+    units += seg[s];
+  }
+}
+
+void OverlapImpl::NcclReduceScatter(at::Tensor C) {
+  // In place: rank r's shard of the sum lands in its own slice of C
+  // (reference: src/overlap_impl.cu:170-179).
+  if (world_ == 1) return;
+  const int64_t recv = C.numel() / world_;
+  char* base = static_cast<char*>(C.data_ptr());
+  FO_NCCL_CHECK(ncclReduceScatter(base, base + rank_ * recv * C.element_size(), recv, nccl_dtype(C),
+                                  ncclSum, comm_, stream()));
+}
+
+void OverlapImpl::NcclAll2All(at::Tensor C, at::Tensor D, at::Tensor mLen_CPU) {
+  // Variable-size all-to-all on packed rows: rank r sends mLen[r][i] rows to rank i and
+  // receives mLen[i][r] rows from it; a rank's own rows are not part of C or D
+  // (reference: src/overlap_impl.cu:181-212).
+  if (world_ == 1) return;
+  TORCH_CHECK(!mLen_CPU.is_cuda() && mLen_CPU.scalar_type() == at::kInt &&
+                  mLen_CPU.numel() == static_cast<int64_t>(world_) * world_,
+              "mLen_CPU must be an int32 host tensor of shape [world, world]");
+  const int* ml = mLen_CPU.data_ptr<int>();
+  const int64_t N = C.size(-1);
+  const size_t es = C.element_size();
+  char* src = static_cast<char*>(C.data_ptr());
+  char* dst = static_cast<char*>(D.data_ptr());
+  int64_t so = 0, ro = 0;
+  FO_NCCL_CHECK(ncclGroupStart());
+  for (int i = 0; i < world_; ++i) {
+    if (i == rank_) continue;
+    const int64_t sc = static_cast<int64_t>(ml[rank_ * world_ + i]) * N;
+    const int64_t rc = static_cast<int64_t>(ml[i * world_ + rank_]) * N;
+    FO_NCCL_CHECK(ncclSend(src + so * es, sc, nccl_dtype(C), i, comm_, stream()));
+    FO_NCCL_CHECK(ncclRecv(dst + ro * es, rc, nccl_dtype(C), i, comm_, stream()));
+    so += sc;
+    ro += rc;
+  }
+  FO_NCCL_CHECK(ncclGroupEnd());
+}
+
+// ---------------------------------------------------------------------------- non-overlapped
+
+void OverlapImpl::GemmAllReduce(at::Tensor A, at::Tensor B, at::Tensor C, int64_t Algo) {
+  Gemm(A, B, C, Algo);
+  NcclAllReduce(C);
+}
+
+void OverlapImpl::GemmReduceScatter(at::Tensor A, at::Tensor B, at::Tensor C, at::Tensor D,
+                                    int64_t Algo) {
+  Gemm(A, B, C, Algo);
+  const int64_t recv = C.numel() / world_;
+  check_out(D, A, recv, "D");
+  if (world_ == 1) {
+    cuda_check(cudaMemcpyAsync(D.data_ptr(), C.data_ptr(), recv * C.element_size(),
+                               cudaMemcpyDeviceToDevice, stream()),
+               "cudaMemcpyAsync");
+    return;
+  }
+  FO_NCCL_CHECK(ncclReduceScatter(C.data_ptr(), D.data_ptr(), recv, nccl_dtype(C), ncclSum, comm_,
+                                  stream()));
+}
+
+void OverlapImpl::GemmAll2All(at::Tensor A, at::Tensor B, at::Tensor C, at::Tensor D, int64_t Algo,
+                              at::Tensor mLen_CPU) {
+  Gemm(A, B, C, Algo);
+  NcclAll2All(C, D, mLen_CPU);
+}
+
+// ---------------------------------------------------------------------------- fused path
+
+void OverlapImpl::ensure_fused_buffers(size_t stage_bytes, size_t nflags) {
+  TORCH_CHECK(heap_ != nullptr, "call nccl_init first");
+  TORCH_CHECK(nflags <= kSignalMaxFlags, "too many tiles/groups for the flag region: ", nflags);
+  if (signal_ == nullptr) signal_ = heap_->allocate(kSignalBytes, stream());
+  if (stage_ == nullptr || stage_->bytes < stage_bytes) {
+    // A larger shape than any seen so far: take a new region (the old one stays mapped until
+    // this object dies, peers may still hold its address).
+    stage_ = heap_->allocate(stage_bytes, stream());
+  }
+}
+
+void OverlapImpl::run_fused(int comm, const at::Tensor& A, const at::Tensor& B, at::Tensor out,
+                            int out_mode, const int* RA, int rldn, int* MM, int mm_stride,
+                            bool monitor, const int* cseg, int num_groups, int algo) {
+  TORCH_CHECK(heap_ != nullptr, "call nccl_init first");
+  c10::cuda::CUDAGuard guard(A.device());
+  TORCH_CHECK(kBM % world_ == 0, "world size must divide the tile height 128");
+  GemmTensorMaps maps;
+  GemmParams p;
+  std::memset(&p, 0, sizeof(p));
+  bool bf16 = true;
+  setup_problem(algo, A, B, 0, &maps, &p, &bf16);
+  TORCH_CHECK(rldn == 1 || comm == kCommFusedAR, "reduce-scatter requires rLDN == 1");
+
+  const size_t full_bytes = static_cast<size_t>(p.M) * p.N * 2;
+  const size_t nflags = (num_groups > 0 && cseg != nullptr) ? num_groups : p.num_tiles;
+  ensure_fused_buffers(full_bytes, nflags);
+
+  const size_t out_bytes = comm == kCommFusedAR ? full_bytes : full_bytes / world_;
+  check_out(out, A, static_cast<int64_t>(out_bytes / 2), comm == kCommFusedAR ? "C" : "D");
+  bool copy_back = false;
+  if (comm == kCommFusedAR) {
+    const SymmetricRegion* reg = heap_->find(out.data_ptr(), out_bytes);
+    if (reg != nullptr) {
+      const size_t off = static_cast<char*>(out.data_ptr()) - static_cast<char*>(reg->local());
+      for (int r = 0; r < world_; ++r) p.dst[r] = static_cast<char*>(reg->ptr[r]) + off;
+    } else {
+      // The caller's tensor is ordinary device memory that peers cannot address: reduce into
+      // a symmetric buffer and copy.  Allocate outputs with symm_empty to avoid the copy.
+      if (out_ == nullptr || out_->bytes < out_bytes) out_ = heap_->allocate(out_bytes, stream());
+      for (int r = 0; r < world_; ++r) p.dst[r] = out_->ptr[r];
+      copy_back = true;
+    }
+  } else {
+    p.dst[rank_] = out.data_ptr();
+  }
+
+  ++epoch_;
+  p.out_mode = out_mode;
+  p.rldn = rldn < 1 ? 1 : rldn;
+  p.monitor = monitor ? 1 : 0;
+  p.mm_stride = mm_stride;
+  p.num_groups = (cseg != nullptr) ? num_groups : 0;
+  p.comm = comm;
+  p.ws = world_;
+  p.rank_base = rank_;
+  p.strided_rows = static_cast<int>(opt_strided_rows_);
+  p.epoch_done_prev = static_cast<uint32_t>(world_) * (epoch_ - 1);
+  p.epoch_done = static_cast<uint32_t>(world_) * epoch_;
+  p.timeout_ns = static_cast<uint64_t>(opt_timeout_ms_) * 1000000ull;
+  p.RA = RA;
+  p.cseg = cseg;
+  p.MM[0] = MM;
+  p.status[0] = status_.data_ptr<int>();
+  p.local_cnt[0] =
+      reinterpret_cast<uint32_t*>(static_cast<char*>(signal_->local()) + kSignalLocalCntOffset);
+  for (int r = 0; r < world_; ++r) {
+    p.stage[r] = stage_->ptr[r];
+    char* sig = static_cast<char*>(signal_->ptr[r]);
+    p.flags[r] = reinterpret_cast<uint32_t*>(sig + kSignalFlagsOffset);
+    p.done[r] = reinterpret_cast<uint32_t*>(sig + kSignalDoneOffset);
+  }
+  const int grid = std::max(1, std::min(sm_count_, p.num_tiles));
+  cuda_check(launch_gemm(algo, bf16, true, maps, p, grid, 1, false, stream()), "fused GEMM launch");
+  if (copy_back) {
+    cuda_check(cudaMemcpyAsync(out.data_ptr(), out_->local(), out_bytes, cudaMemcpyDeviceToDevice,
+                               stream()),
+               "cudaMemcpyAsync");
+  }
+}
+
+void OverlapImpl::GemmAllReduceFused(at::Tensor A, at::Tensor B, at::Tensor C, int64_t Algo) {
+  if (world_ == 1) {
+    Gemm(A, B, C, Algo);
+    return;
+  }
+  run_fused(kCommFusedAR, A, B, C, kOutNatural, nullptr, 1, nullptr, 0, false, nullptr, 0,
+            static_cast<int>(Algo));
+}
+
+void OverlapImpl::GemmReduceScatterFused(at::Tensor A, at::Tensor B, at::Tensor D, int64_t Algo) {
+  if (world_ == 1) {
+    Gemm(A, B, D, Algo);
+    return;
+  }
+  run_fused(kCommFusedRS, A, B, D, kOutNatural, nullptr, 1, nullptr, 0, false, nullptr, 0,
+            static_cast<int>(Algo));
+}
+
+// ---------------------------------------------------------------------------- reference API
+
+namespace {
+int* mm_ptr(const at::Tensor& MM) {
+  TORCH_CHECK(MM.is_cuda() && MM.scalar_type() == at::kInt && MM.is_contiguous(),
+              "MM must be a contiguous int32 CUDA tensor");
+  return MM.data_ptr<int>();
+}
+}  // namespace
+
+void OverlapImpl::GemmAllReduceOverlap(at::Tensor A, at::Tensor B, at::Tensor C, at::Tensor MM,
+                                       at::Tensor RA, int64_t rLDN, at::Tensor cSEG_CPU,
+                                       at::Tensor cSEG_GPU, int64_t Algo, bool if_monitor) {
+  const GemmShape s = check_operands(A, B);
+  check_out(C, A, static_cast<int64_t>(s.M) * s.N, "C");
+  const AlgoConfig c = algo_config(static_cast<int>(Algo));
+  const int tn = s.N / c.bn;
+  const int* ra = int_ptr_or_null(RA, "RA");
+  const int* cseg = int_ptr_or_null(cSEG_GPU, "cSEG_GPU");
+  const int ngroups = cseg != nullptr ? static_cast<int>(cSEG_GPU.numel()) : 0;
+  if (opt_mode_ == 1 && world_ > 1) {
+    gated_overlap(kCommFusedAR, A, B, C, at::Tensor(), MM, RA, at::Tensor(), rLDN, cSEG_CPU,
+                  cSEG_GPU, Algo, if_monitor);
+    return;
+  }
+  if (world_ == 1) {
+    // AllReduce over one rank is the identity: the reordered GEMM alone.
+    run_plain(A, B, C.data_ptr(), kOutReorder, ra, nullptr, static_cast<int>(rLDN),
+              if_monitor ? mm_ptr(MM) : nullptr, tn, false, if_monitor, cseg, ngroups,
+              static_cast<int>(Algo), sm_count_);
+    return;
+  }
+  run_fused(kCommFusedAR, A, B, C, kOutReorder, ra, static_cast<int>(rLDN),
+            if_monitor ? mm_ptr(MM) : nullptr, tn, if_monitor, cseg, ngroups,
+            static_cast<int>(Algo));
+}
+
+void OverlapImpl::GemmReduceScatterOverlap(at::Tensor A, at::Tensor B, at::Tensor C, at::Tensor D,
+                                           at::Tensor MM, at::Tensor RA, at::Tensor RE,
+                                           int64_t rLDN, at::Tensor cSEG_CPU, at::Tensor cSEG_GPU,
+                                           int64_t Algo, bool if_monitor) {
+  const GemmShape s = check_operands(A, B);
+  check_out(D, A, static_cast<int64_t>(s.M) * s.N / world_, "D");
+  const AlgoConfig c = algo_config(static_cast<int>(Algo));
+  const int tn = s.N / c.bn;
+  const int* ra = int_ptr_or_null(RA, "RA");
+  const int* cseg = int_ptr_or_null(cSEG_GPU, "cSEG_GPU");
+  const int ngroups = cseg != nullptr ? static_cast<int>(cSEG_GPU.numel()) : 0;
+  TORCH_CHECK(rLDN == 1, "reduce-scatter requires rLDN == 1");
+  if (opt_mode_ == 1 && world_ > 1) {
+    gated_overlap(kCommFusedRS, A, B, C, D, MM, RA, RE, rLDN, cSEG_CPU, cSEG_GPU, Algo, if_monitor);
+    return;
+  }
+  if (world_ == 1) {
+    run_plain(A, B, D.data_ptr(), kOutReorder, ra, nullptr, 1, if_monitor ? mm_ptr(MM) : nullptr, tn,
+              false, if_monitor, cseg, ngroups, static_cast<int>(Algo), sm_count_);
+    return;
+  }
+  // C (the reference's full-size scratch) is not needed: partial tiles go straight to the
+  // owners' staging memory.
+  run_fused(kCommFusedRS, A, B, D, kOutReorder, ra, 1, if_monitor ? mm_ptr(MM) : nullptr, tn,
+            if_monitor, cseg, ngroups, static_cast<int>(Algo));
+}
+
+// The reference's mechanism on our GEMM: signalling GEMM on the caller's stream; on the
+// communication stream one bounded counting wait plus one NCCL call per wave group
+// (src/overlap_impl.cu:247-263, :303-320).  Baseline for the fused kernels.
+void OverlapImpl::gated_overlap(int comm, at::Tensor A, at::Tensor B, at::Tensor C, at::Tensor D,
+                                at::Tensor MM, at::Tensor RA, at::Tensor RE, int64_t rLDN,
+                                at::Tensor cSEG_CPU, at::Tensor cSEG_GPU, int64_t Algo,
+                                bool monitor) {
+  ensure_comm_stream();
+  const GemmShape s = check_operands(A, B);
+  check_out(C, A, static_cast<int64_t>(s.M) * s.N, "C");
+  const AlgoConfig c = algo_config(static_cast<int>(Algo));
+  const int tn = s.N / c.bn;
+  const int tiles = (s.M / c.bm) * tn;
+  TORCH_CHECK(!cSEG_CPU.is_cuda() && cSEG_CPU.scalar_type() == at::kInt, "cSEG_CPU: int32 host tensor");
+  const int* seg = cSEG_CPU.data_ptr<int>();
+  const int ngroups = static_cast<int>(cSEG_CPU.numel());
+  const int* cseg_gpu = int_ptr_or_null(cSEG_GPU, "cSEG_GPU");
+  TORCH_CHECK(cseg_gpu != nullptr && cSEG_GPU.numel() == ngroups, "cSEG_GPU must mirror cSEG_CPU");
+  int* mm = mm_ptr(MM);
+  TORCH_CHECK(MM.numel() >= ngroups, "MM has fewer counters than there are groups");
+  const bool rs = comm == kCommFusedRS;
+  const int* re = rs ? int_ptr_or_null(RE, "RE") : nullptr;
+  TORCH_CHECK(!rs || re != nullptr, "RE is required for reduce-scatter");
+
+  cudaStream_t gs = stream();
+  // Counters are consumed by this call only once the GEMM stream has reached this point
+  // (the reference lets the two streams race from the start and relies on the counters
+  // alone; ordering the streams also makes MM zeroing by earlier work safe).
+  cuda_check(cudaEventRecord(gemm_start_, gs), "cudaEventRecord");
+  cuda_check(cudaStreamWaitEvent(comm_stream_, gemm_start_, 0), "cudaStreamWaitEvent");
+
+  run_plain(A, B, C.data_ptr(), rs ? kOutScatterRows : kOutReorder, int_ptr_or_null(RA, "RA"), re,
+            static_cast<int>(rLDN), mm, tn, true, monitor, cseg_gpu, ngroups,
+            static_cast<int>(Algo), sm_count_ - static_cast<int>(opt_sm_margin_));
+
+  const size_t es = C.element_size();
+  const int64_t tile_elems = static_cast<int64_t>(c.bm) * c.bn;
+  char* cb = static_cast<char*>(C.data_ptr());
+  char* db = rs ? static_cast<char*>(D.data_ptr()) : nullptr;
+  const uint64_t timeout_ns = static_cast<uint64_t>(opt_timeout_ms_) * 1000000ull;
+  int64_t acc = 0;
+  int covered = 0;
+  for (int g = 0; g < ngroups && covered < tiles; ++g) {
+    const int64_t n = tile_elems * seg[g];
+    cuda_check(wait_flag_launch(seg[g], mm + g, g, timeout_ns, status_.data_ptr<int>(), comm_stream_),
+               "wait kernel launch");
+    if (rs) {
+      FO_NCCL_CHECK(ncclReduceScatter(cb + acc * es, db + (acc / world_) * es, n / world_,
+                                      nccl_dtype(C), ncclSum, comm_, comm_stream_));
+    } else {
+      FO_NCCL_CHECK(ncclAllReduce(cb + acc * es, cb + acc * es, n, nccl_dtype(C), ncclSum, comm_,
+                                  comm_stream_));
+    }
+    acc += n;
+    covered += seg[g];
+  }
+  cuda_check(cudaEventRecord(comm_done_, comm_stream_), "cudaEventRecord");
+  cuda_check(cudaStreamWaitEvent(gs, comm_done_, 0), "cudaStreamWaitEvent");
+}
+
+}  // namespace fo

@@ -1,0 +1,109 @@
+// Host runtime of the overlap path: owns the NCCL communicator, the streams, the symmetric
+// staging/flag memory and launches the tcgen05 GEMM family.
+//
+// The method set and argument orders follow the reference class (src/overlap_impl.h:12-43,
+// bound at src/pybind.cpp:129-144) so that its callers run unchanged.  What differs is the
+// mechanism behind gemm_allreduce_overlap / gemm_reducescatter_overlap: by default they run
+// ONE kernel that computes the tiles and performs the collective over NVLink peer memory.
+// The reference's mechanism - signalling GEMM on one stream, counting wait kernel plus one
+// NCCL call per wave group on a second stream (src/overlap_impl.cu:214-321) - is kept as
+// mode "gated" and serves as a baseline.
+#pragma once
+#include <ATen/ATen.h>
+#include <cuda_runtime.h>
+#include <nccl.h>
+#include <torch/custom_class.h>
+
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "../comm/symmetric_heap.h"
+#include "../gemm/fo_gemm_params.h"
+
+namespace fo {
+
+class OverlapImpl : public torch::CustomClassHolder {
+ public:
+  OverlapImpl();
+  ~OverlapImpl() override;
+
+  // ---- reference API (names as bound in Python; see binding.cpp) ----
+  void NcclInit(int64_t rank, int64_t world, std::vector<int64_t> id);
+  void CutlassInit();  // name kept for compatibility: captures torch's current stream
+  void OverlapInit();  // creates the high-priority communication stream
+  void Gemm(at::Tensor A, at::Tensor B, at::Tensor C, int64_t Algo);
+  void GemmAllReduce(at::Tensor A, at::Tensor B, at::Tensor C, int64_t Algo);
+  void GemmReduceScatter(at::Tensor A, at::Tensor B, at::Tensor C, at::Tensor D, int64_t Algo);
+  void GemmAll2All(at::Tensor A, at::Tensor B, at::Tensor C, at::Tensor D, int64_t Algo,
+                   at::Tensor mLen_CPU);
+  void NcclAllReduce(at::Tensor C);
+  void SegAllReduce(at::Tensor C, at::Tensor cSEG_CPU, int64_t SegNum);
+  void NcclReduceScatter(at::Tensor C);
+  void NcclAll2All(at::Tensor C, at::Tensor D, at::Tensor mLen_CPU);
+  void GemmAllReduceOverlap(at::Tensor A, at::Tensor B, at::Tensor C, at::Tensor MM, at::Tensor RA,
+                            int64_t rLDN, at::Tensor cSEG_CPU, at::Tensor cSEG_GPU, int64_t Algo,
+                            bool if_monitor);
+  void GemmReduceScatterOverlap(at::Tensor A, at::Tensor B, at::Tensor C, at::Tensor D,
+                                at::Tensor MM, at::Tensor RA, at::Tensor RE, int64_t rLDN,
+                                at::Tensor cSEG_CPU, at::Tensor cSEG_GPU, int64_t Algo,
+                                bool if_monitor);
+
+  // ---- additions ----
+  // Fused collectives with row-major results and one flag per tile: no RA / cSeg needed.
+  void GemmAllReduceFused(at::Tensor A, at::Tensor B, at::Tensor C, int64_t Algo);
+  void GemmReduceScatterFused(at::Tensor A, at::Tensor B, at::Tensor D, int64_t Algo);
+  // Options: "mode" (0 fused, 1 gated), "strided_rows" (reduce-scatter row ownership:
+  // 1 = rank r owns rows i % world == r as in the reference, 0 = contiguous blocks),
+  // "sm_margin" (SMs left to NCCL in gated mode), "timeout_ms" (bound of device waits).
+  void SetOption(std::string name, int64_t value);
+  int64_t GetOption(std::string name);
+  // Collective allocation of a tensor in symmetric memory.  AllReduce results written into
+  // such a tensor need no extra copy.
+  at::Tensor SymmEmpty(std::vector<int64_t> sizes, std::string dtype);
+  // Status words written by device-side waits that gave up (all zero when healthy).
+  std::vector<int64_t> ReadStatus();
+  void CheckStatus();  // throws with a description when the status is not ok
+  void ResetStatus();  // clears status and re-arms flags after a reported failure
+
+ private:
+  struct FusedArgs;
+  void run_plain(const at::Tensor& A, const at::Tensor& B, void* out, int out_mode,
+                 const int* RA, const int* RE, int rldn, int* MM, int mm_stride, bool signal,
+                 bool monitor, const int* cseg, int num_groups, int algo, int grid_cap);
+  void run_fused(int comm, const at::Tensor& A, const at::Tensor& B, at::Tensor out, int out_mode,
+                 const int* RA, int rldn, int* MM, int mm_stride, bool monitor, const int* cseg,
+                 int num_groups, int algo);
+  void gated_overlap(int comm, at::Tensor A, at::Tensor B, at::Tensor C, at::Tensor D,
+                     at::Tensor MM, at::Tensor RA, at::Tensor RE, int64_t rLDN,
+                     at::Tensor cSEG_CPU, at::Tensor cSEG_GPU, int64_t Algo, bool monitor);
+  void ensure_fused_buffers(size_t stage_bytes, size_t nflags);
+  void ensure_comm_stream();
+  cudaStream_t stream() const;
+  ncclDataType_t nccl_dtype(const at::Tensor& t) const;
+
+  int rank_ = 0;
+  int world_ = 1;
+  int device_ = 0;
+  int sm_count_ = 148;
+  ncclComm_t comm_ = nullptr;
+  bool have_gemm_stream_ = false;
+  cudaStream_t gemm_stream_ = nullptr;
+  cudaStream_t comm_stream_ = nullptr;
+  cudaEvent_t comm_done_ = nullptr;
+  cudaEvent_t gemm_start_ = nullptr;
+
+  std::unique_ptr<SymmetricHeap> heap_;
+  SymmetricRegion* stage_ = nullptr;
+  SymmetricRegion* signal_ = nullptr;
+  SymmetricRegion* out_ = nullptr;  // symmetric AllReduce output when the caller's is not
+  uint32_t epoch_ = 0;
+  at::Tensor status_;  // int32[kStatusWords] on the device
+
+  int64_t opt_mode_ = 0;
+  int64_t opt_strided_rows_ = 1;
+  int64_t opt_sm_margin_ = 16;
+  int64_t opt_timeout_ms_ = 2000;
+};
+
+}  // namespace fo
