@@ -1,0 +1,430 @@
+#!/usr/bin/env python
+"""Headline benchmark: fused GEMM+AllReduce of a row-parallel down-projection.
+
+Config (fixed total work, split over the GPUs = strong scaling): per-rank A[M=8192, K=28672/tp]
+and B[N=8192, K/tp], bf16 ~N(0, 0.02), fp32 accumulate, all-reduced output [8192, 8192] bf16.
+One step = one ``OverlapImpl.gemm_allreduce_overlap`` call (one hand-written sm_100a kernel
+that computes the tiles and all-reduces them over NVLink peer memory).  The value is the
+whole-job rate 2*M*N*K_total / step time in TFLOP/s.
+
+    python bench.py --gpus 1 --steps 200 --warmup 10
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
+        --master-port 29555 bench.py --gpus 8
+
+Rank 0 prints ONE JSON line.  ``--impl reference`` runs the unmodified reference library from
+``baseline/_ref`` through its own ``OverlapImpl`` for the same shape (fp16: it has no bf16).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+M_AR, N_AR, K_AR_TOTAL = 8192, 8192, 28672
+M_RS, N_RS, K_RS_TOTAL = 16384, 8192, 8192
+NVLINK_GBS = 770.0           # measured peer-copy bandwidth per direction per GPU on this pool
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def load_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            d = json.load(f)
+        d["source"] = "measured"
+        return d
+    d = dict(FALLBACK_PEAKS)
+    d["source"] = "fallback"
+    return d
+
+
+class ClockSampler:
+    """Samples SM clock, power and throttle reasons of one GPU with nvidia-smi while timing."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index: int):
+        import torch
+        self.uuid = None
+        try:
+            u = str(torch.cuda.get_device_properties(device_index).uuid)
+            self.uuid = u if u.startswith("GPU-") else "GPU-" + u
+        except Exception:
+            pass
+        self.index = device_index
+        self.proc = None
+        self.file = None
+
+    def start(self):
+        try:
+            self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+            sel = ["-i", self.uuid] if self.uuid else ["-i", str(self.index)]
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", *sel, f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=self.file, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        time.sleep(0.12)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        self.file.flush()
+        self.file.seek(0)
+        sm, mx, pw, reasons = [], [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.file.read().splitlines():
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0])); mx.append(float(parts[1])); pw.append(float(parts[2]))
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        try:
+            os.unlink(self.file.name)
+        except OSError:
+            pass
+        if sm:
+            out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons),
+                       samples=len(sm), power_w_max=max(pw))
+        return out
+
+
+def pick_algo(torch, dist, world, run, candidates, reps=3):
+    """Fastest Algo by a short timing, agreed on by all ranks (max over ranks per candidate)."""
+    times = []
+    for a in candidates:
+        try:
+            for _ in range(2):
+                run(a)
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
+            s.record()
+            for _ in range(reps):
+                run(a)
+            e.record()
+            torch.cuda.synchronize()
+            times.append(s.elapsed_time(e) / reps)
+        except Exception:
+            times.append(1e9)
+    t = torch.tensor(times, device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return candidates[int(t.argmin().item())], [round(x, 4) for x in t.tolist()]
+
+
+def time_steps(torch, dist, world, fn, steps, warmup, flush, sampler=None):
+    """Per-step CUDA events on the launching stream, L2 flushed between steps (outside the
+    event pairs), barrier + synchronize on both sides.  Returns (mean ms over steps, max over
+    ranks), the clock record and the wall time of the bracket."""
+    for _ in range(warmup):
+        fn()
+        flush()
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    if sampler:
+        sampler.start()
+    t0 = time.perf_counter()
+    for s, e in ev:
+        flush()
+        s.record()
+        fn()
+        e.record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - t0
+    clocks = sampler.stop() if sampler else None
+    ms = sum(s.elapsed_time(e) for s, e in ev) / steps
+    t = torch.tensor([ms], device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item()), clocks, wall
+
+
+def e2e_pipeline(torch, dist, world, host_in, dev_bufs, step_on, result_slice, host_out, steps, warmup):
+    """End-to-end loop through the public API: every step copies its input from pinned host
+    memory, runs, and reads a slice of the result back.  The copy of step i+1 overlaps the
+    compute of step i (two device input buffers, one copy stream)."""
+    main = torch.cuda.current_stream()
+    copy = torch.cuda.Stream()
+    ready = [torch.cuda.Event() for _ in dev_bufs]
+    free = [torch.cuda.Event() for _ in dev_bufs]
+
+    def run(n):
+        for i in range(n):
+            b = i % len(dev_bufs)
+            with torch.cuda.stream(copy):
+                copy.wait_event(free[b])
+                dev_bufs[b].copy_(host_in, non_blocking=True)
+                ready[b].record(copy)
+            main.wait_event(ready[b])
+            out = step_on(dev_bufs[b])
+            free[b].record(main)
+            host_out.copy_(result_slice(out), non_blocking=True)
+
+    for f in free:
+        f.record(main)
+    run(warmup)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record(main)
+    run(steps)
+    e.record(main)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    t = torch.tensor([s.elapsed_time(e) / steps], device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def make_flusher(torch):
+    buf = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")  # > 126 MB L2
+    return lambda: buf.zero_()
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    from flashoverlap_b200 import ops
+    from flashoverlap_b200.parallel import bootstrap
+    from flashoverlap_b200.utils import config, layout
+
+    rank, world, local = bootstrap.init_distributed()
+    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}"
+    dev = torch.device("cuda", local)
+    peaks = load_peaks()
+    torch.manual_seed(1234 + rank)
+    flush = make_flusher(torch)
+    impl = bootstrap.make_overlap_impl(rank, world)
+    impl.set_option("timeout_ms", 20000)
+
+    M, N, K = M_AR, N_AR, K_AR_TOTAL // world
+    A = (torch.randn(M, K, device=dev) * 0.02).to(torch.bfloat16)
+    B = (torch.randn(N, K, device=dev) * 0.02).to(torch.bfloat16)
+    C = impl.symm_empty([M, N], "bfloat16") if world > 1 else torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+
+    state = {}
+
+    def prepare(algo):
+        if algo in state:
+            return state[algo]
+        cfg = config.default_solution(M, N, algo)
+        tiles = (M // cfg["BM"]) * (N // cfg["BN"])
+        RA = layout.reorder_indices(tiles, cfg["hint"], device=dev).reshape(M // cfg["BM"], N // cfg["BN"])
+        mm = torch.zeros(1, max(N // cfg["BN"], 8), device=dev, dtype=torch.int32)
+        state[algo] = (cfg, RA, mm)
+        return state[algo]
+
+    empty = torch.empty(0, dtype=torch.int32)
+    empty_gpu = torch.empty(0, dtype=torch.int32, device=dev)
+
+    def step_algo(algo, a=A):
+        cfg, RA, mm = prepare(algo)
+        # per-tile flags (empty cSeg): the finest wave grouping, which the fused kernel prefers
+        impl.gemm_allreduce_overlap(a, B, C, mm, RA, 1, empty, empty_gpu, algo, False)
+        return C
+
+    tuned_path = config.config_path(M, N, K, "b200")
+    if os.path.exists(tuned_path) and config.is_tuned(config.load_config(tuned_path)):
+        algo, algo_times = int(config.load_config(tuned_path)["Algo"]), None
+    else:
+        algo, algo_times = pick_algo(torch, dist, world, step_algo, [0, 4, 8, 16, 20])
+
+    sampler = ClockSampler(local) if rank == 0 else None
+    ms, clocks, wall = time_steps(torch, dist, world, lambda: step_algo(algo), args.steps, args.warmup, flush, sampler)
+    impl.check_status()
+    flops = 2.0 * M * N * K_AR_TOTAL
+    value = flops / (ms * 1e-3) / 1e12
+
+    # correctness spot check of the timed path against torch (row block 0, fp32 reference)
+    cfg, RA, _ = prepare(algo)
+    nat = ops.unreorder(C, M, N, cfg["BM"], cfg["BN"], RA)
+    ref = A[:128].float() @ B.float().t()
+    if world > 1:
+        dist.all_reduce(ref)
+    check_err = float((nat[:128].float() - ref).abs().max().item())
+
+    # ---- end to end: pinned host input every step, result slice read back every step
+    host_in = torch.empty(M, K, dtype=torch.bfloat16).pin_memory()
+    host_in.copy_(A)
+    host_out = torch.empty(128, N, dtype=torch.bfloat16).pin_memory()
+    dev_bufs = [torch.empty_like(A), torch.empty_like(A)]
+    e2e_steps = max(3, min(args.steps, 30))
+    e2e_ms = e2e_pipeline(torch, dist, world, host_in, dev_bufs, lambda a: step_algo(algo, a),
+                          lambda out: out.view(-1)[: 128 * N].view(128, N), host_out, e2e_steps,
+                          max(3, min(args.warmup, 5)))
+    impl.check_status()
+
+    # ---- roofline of the fused step
+    S = M * N * 2
+    t_gemm = 2.0 * M * N * K / (peaks["bf16_tflops"] * 1e12)
+    t_link = (2.0 * S * (world - 1) / world) / (NVLINK_GBS * 1e9) if world > 1 else 0.0
+    roof_ms = max(t_gemm, t_link) * 1e3
+
+    extra = {"algo": algo, "algo_probe_ms": algo_times, "check_max_abs_err": check_err,
+             "roofline_ms": round(roof_ms, 4), "roofline_frac": round(roof_ms / ms, 4),
+             "roofline_peaks": peaks["source"], "wall_s_timed_region": round(wall, 3)}
+
+    if not args.no_extra:
+        try:
+            extra.update(extras(torch, dist, impl, rank, world, dev, A, B, C, algo, flush, peaks))
+        except Exception as ex:  # extras never block the headline line
+            extra["extras_error"] = repr(ex)[:300]
+
+    line = {
+        "metric": "gemm_allreduce_tflops", "value": round(value, 2), "unit": "TFLOP/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 5),
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic", "impl": "ours",
+        "config": {"model": "row-parallel down-proj GEMM+AllReduce (Llama-3-70B MLP shape)",
+                   "M": M, "N": N, "K_total": K_AR_TOTAL, "K_per_rank": K, "global_batch": M, "seq_len": None,
+                   "parallelism": f"tp{world}", "l2": "256 MB buffer written between timed steps",
+                   "timing": "per-step CUDA events on the launching stream, mean over steps, max over ranks"},
+        "clocks": clocks,
+        "e2e": {"value": round(flops / (e2e_ms * 1e-3) / 1e12, 2), "unit": "TFLOP/s", "ms_per_step": round(e2e_ms, 5),
+                "steps": e2e_steps, "h2d_bytes_per_step": M * K * 2, "d2h_bytes_per_step": 128 * N * 2,
+                "note": "input copied from pinned host memory every step (double-buffered, overlapping "
+                        "the previous step's kernel); first 128 result rows read back every step"},
+        "gpu_launches": args.steps * 1,
+        "extra": extra,
+    }
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def extras(torch, dist, impl, rank, world, dev, A, B, C, algo, flush, peaks):
+    """Comparison arms on the same box: our GEMM then one NCCL call (non-overlap), cuBLAS + NCCL,
+    the counter-gated NCCL mechanism, and the GEMM+ReduceScatter+RMSNorm config."""
+    from flashoverlap_b200 import ops
+    from flashoverlap_b200.parallel import bootstrap
+    from flashoverlap_b200.utils import config, layout
+
+    out = {}
+    steps, warm = 20, 5
+    M, N = A.shape[0], B.shape[0]
+    Cn = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+    ms, _, _ = time_steps(torch, dist, world, lambda: impl.gemm_allreduce(A, B, Cn, algo), steps, warm, flush)
+    out["nonoverlap_ourgemm_nccl_ms"] = round(ms, 5)
+    base = bootstrap.make_baseline_impl(rank, world)
+    ms, _, _ = time_steps(torch, dist, world, lambda: base.gemm_allreduce(A, B, Cn), steps, warm, flush)
+    out["cublas_nccl_ms"] = round(ms, 5)
+    ms, _, _ = time_steps(torch, dist, world, lambda: base.cublas_gemm(A, B, Cn), steps, warm, flush)
+    out["cublas_gemm_only_ms"] = round(ms, 5)
+    ms, _, _ = time_steps(torch, dist, world, lambda: impl.cutlass_gemm(A, B, Cn, algo), steps, warm, flush)
+    out["our_gemm_only_ms"] = round(ms, 5)
+    if world > 1:
+        cfg = config.default_solution(M, N, algo, wave_size=148 - 16)
+        tiles = (M // cfg["BM"]) * (N // cfg["BN"])
+        nw = layout.div_up(tiles, 148 - 16)
+        groups = [nw // 4 + (1 if i < nw % 4 else 0) for i in range(4)] if nw >= 4 else [1] * nw
+        cseg = layout.cseg_from_wave_groups(tiles, 148 - 16, groups)
+        RA = layout.reorder_indices(tiles, cfg["hint"], device=dev)
+        mm = torch.zeros(1, max(N // cfg["BN"], len(cseg)), device=dev, dtype=torch.int32)
+        cseg_cpu = torch.tensor(cseg, dtype=torch.int32)
+        cseg_gpu = cseg_cpu.to(dev)
+        impl.set_option("mode", 1)
+        try:
+            ms, _, _ = time_steps(torch, dist, world,
+                                  lambda: impl.gemm_allreduce_overlap(A, B, Cn, mm, RA, 1, cseg_cpu, cseg_gpu, algo, False),
+                                  steps, warm, flush)
+            out["gated_nccl_ms"] = round(ms, 5)
+        finally:
+            impl.set_option("mode", 0)
+
+    # GEMM + ReduceScatter + RMSNorm (sequence-parallel o_proj shape)
+    M2, N2, K2 = M_RS, N_RS, K_RS_TOTAL // world
+    A2 = (torch.randn(M2, K2, device=dev) * 0.02).to(torch.bfloat16)
+    B2 = (torch.randn(N2, K2, device=dev) * 0.02).to(torch.bfloat16)
+    w = (1 + 0.02 * torch.randn(N2, device=dev)).to(torch.bfloat16)
+    D = torch.empty(M2 // world, N2, device=dev, dtype=torch.bfloat16)
+    Y = torch.empty_like(D)
+    cfg = config.default_solution(M2, N2, algo)
+    tiles = (M2 // cfg["BM"]) * (N2 // cfg["BN"])
+    RA = layout.reorder_indices(tiles, cfg["hint"], device=dev)
+    mm = torch.zeros(1, N2 // cfg["BN"], device=dev, dtype=torch.int32)
+    empty, empty_gpu = torch.empty(0, dtype=torch.int32), torch.empty(0, dtype=torch.int32, device=dev)
+    bm_local = cfg["BM"] // world
+
+    def rs_step():
+        impl.gemm_reducescatter_overlap(A2, B2, D, D, mm, RA, empty_gpu, 1, empty, empty_gpu, algo, False)
+        torch.ops.flashoverlap_op.reorder_rmsnorm_eps(D, Y, w, bm_local, cfg["BN"], 1, RA, 1e-5)
+
+    ms, _, _ = time_steps(torch, dist, world, rs_step, steps, warm, flush)
+    S2 = M2 * N2 * 2
+    t_gemm = 2.0 * M2 * N2 * K2 / (peaks["bf16_tflops"] * 1e12)
+    t_link = (S2 * (world - 1) / world) / (NVLINK_GBS * 1e9) if world > 1 else 0.0
+    t_norm = 2.0 * (S2 / world) / (peaks["hbm_gbs"] * 1e9)
+    rs = {"ms": round(ms, 5), "roofline_ms": round((max(t_gemm, t_link) + t_norm) * 1e3, 4), "M": M2, "N": N2, "K_per_rank": K2}
+    C2 = torch.empty(M2, N2, device=dev, dtype=torch.bfloat16)
+
+    def rs_base():
+        base.gemm_reducescatter(A2, B2, C2, D)
+        torch.ops.flashoverlap_op.rmsnorm(D, Y, w, 1e-5)
+
+    msb, _, _ = time_steps(torch, dist, world, rs_base, steps, warm, flush)
+    rs["cublas_nccl_rmsnorm_ms"] = round(msb, 5)
+    rs["speedup_vs_cublas_nccl"] = round(msb / ms, 4)
+    out["rs_rmsnorm"] = rs
+    if "cublas_nccl_ms" in out:
+        pass
+    impl.check_status()
+    return out
+
+
+def run_reference(args):
+    from baseline import reference_arm
+    reference_arm.main(args)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--no-extra", action="store_true", help="skip the comparison arms")
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,79 @@
+"""Python-side handles on the native ops.
+
+Every function here goes to a hand-written sm_100a kernel through ``torch.ops.flashoverlap_op``
+(csrc/binding.cpp).  There is no PyTorch fallback for CUDA tensors: if the extension cannot
+be loaded the call raises, so a GPU run can never silently measure eager code.
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence
+
+import torch
+
+from .._build import load as _load
+
+
+def _op():
+    _load()
+    return torch.ops.flashoverlap_op
+
+
+def OverlapImpl():
+    _load()
+    return torch.classes.flashoverlap_class.OverlapImpl()
+
+
+def BaselineImpl():
+    _load()
+    return torch.classes.flashoverlap_class.BaselineImpl()
+
+
+def generate_nccl_id() -> List[int]:
+    return list(_op().generate_nccl_id())
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-5, out: Optional[torch.Tensor] = None):
+    x2 = x.reshape(-1, x.shape[-1]).contiguous()
+    out = torch.empty_like(x2) if out is None else out
+    _op().rmsnorm(x2, out, weight, eps)
+    return out.view(x.shape)
+
+
+def reorder_rmsnorm(x_reordered: torch.Tensor, rows: int, dim: int, weight: torch.Tensor, BM: int, BN: int,
+                    RA: torch.Tensor, eps: float = 1e-5, rldn: int = 1, out: Optional[torch.Tensor] = None):
+    out = torch.empty((rows, dim), dtype=x_reordered.dtype, device=x_reordered.device) if out is None else out
+    _op().reorder_rmsnorm_eps(x_reordered, out, weight, BM, BN, rldn, RA, eps)
+    return out
+
+
+def reorder(x: torch.Tensor, BM: int, BN: int, RA: torch.Tensor, rldn: int = 1, out: Optional[torch.Tensor] = None):
+    """Row-major [rows, dim] -> tile-contiguous buffer (tile t at position RA[t])."""
+    out = torch.empty_like(x) if out is None else out
+    _op().reorder(x.contiguous(), out, BM, BN, rldn, RA)
+    return out
+
+
+def unreorder(x_reordered: torch.Tensor, rows: int, dim: int, BM: int, BN: int, RA: torch.Tensor, rldn: int = 1,
+              out: Optional[torch.Tensor] = None):
+    out = torch.empty((rows, dim), dtype=x_reordered.dtype, device=x_reordered.device) if out is None else out
+    _op().unreorder(x_reordered, out, BM, BN, rldn, RA)
+    return out
+
+
+def wait_flag(target: int, counters: torch.Tensor, index: int, timeout_ms: int, status: torch.Tensor) -> None:
+    _op().wait_flag(target, counters, index, timeout_ms, status)
+
+
+def algo_table() -> List[Sequence[int]]:
+    flat = list(_op().algo_table())
+    return [tuple(flat[i:i + 5]) for i in range(0, len(flat), 5)]
+
+
+def fused_loopback(comm_op: str, A: List[torch.Tensor], B: List[torch.Tensor], out: List[torch.Tensor],
+                   RA: Optional[torch.Tensor] = None, cseg: Optional[torch.Tensor] = None, algo: int = 0,
+                   strided_rows: bool = True, natural_out: bool = True, repeat: int = 1,
+                   timeout_ms: int = 1000) -> List[List[int]]:
+    """All ranks of a fused GEMM+collective on ONE GPU in one cooperative launch (test aid)."""
+    flat = list(_op().fused_loopback(comm_op, A, B, out, RA, cseg, algo, strided_rows, natural_out, repeat,
+                                     timeout_ms))
+    return [flat[i:i + 8] for i in range(0, len(flat), 8)]

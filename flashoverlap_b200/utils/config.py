@@ -1,0 +1,115 @@
+"""The on-disk tuning state: ``configs/m{M}n{N}k{K}_{gpu}.json``, ``AlgoDict.pt`` and the
+bandwidth curves - same names and keys as the reference so configs remain interchangeable
+in shape (tune/profile_config.py:57-72, tune/search.py:20-51, tune/bandwidth.py:111,
+tool/generate_instances.py:40-45).
+
+Stage 1 (``gen_config`` / ``profile_config``) writes lists of the 10 fastest GEMM configs:
+``{"BM": [...], "BN": [...], "dur": [...], "Algo": [...]}``.  ``search`` rewrites the file with
+scalars plus ``hint`` (natural tile ids in completion order), ``cSeg`` (tiles per wave group)
+and ``rLDN``.  Keys this library adds (``tp``, ``comm_op``, ``dtype``, ``mode``) are optional
+and ignored by readers that do not know them.
+"""
+from __future__ import annotations
+
+import json
+import os
+from pathlib import Path
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+# (BM, BN, BK, stages, raster strip) of every Algo index; must match algo_config() in
+# csrc/gemm/fo_gemm_params.h (checked against the native table by tests/test_config.py
+# whenever the library is loaded).
+_KERNELS = [(256, 4), (256, 3), (128, 6), (128, 4)]
+_RASTERS = [8, 4, 2, 1, 16, 0]
+NUM_ALGOS = len(_KERNELS) * len(_RASTERS)
+BM = 128
+BK = 64
+
+
+def algo_params(algo: int) -> Dict[str, int]:
+    if not 0 <= algo < NUM_ALGOS:
+        raise ValueError(f"Algo {algo} out of range [0, {NUM_ALGOS})")
+    bn, stages = _KERNELS[algo & 3]
+    return {"BM": BM, "BN": bn, "BK": BK, "stages": stages, "raster": _RASTERS[algo >> 2]}
+
+
+def algo_tuple(algo: int) -> Tuple[int, ...]:
+    """12-tuple key of AlgoDict, the slot meaning adapted to a tcgen05 kernel:
+    (BM, BN, BK, UMMA_M, UMMA_N, UMMA_K, cta_group, accumulator stages, epilogue chunk,
+    pipeline stages, raster strip, split-K)."""
+    p = algo_params(algo)
+    return (p["BM"], p["BN"], p["BK"], 128, p["BN"], 16, 1, 2, 64, p["stages"], p["raster"], 1)
+
+
+def algo_dict() -> Dict[Tuple[int, ...], int]:
+    return {algo_tuple(a): a for a in range(NUM_ALGOS)}
+
+
+def default_config_dir() -> Path:
+    return Path(os.environ.get("FLASHOVERLAP_CONFIG_DIR", Path(__file__).resolve().parents[2] / "configs"))
+
+
+def save_algo_dict(path: Optional[os.PathLike] = None) -> Path:
+    path = Path(path) if path else default_config_dir() / "AlgoDict.pt"
+    path.parent.mkdir(parents=True, exist_ok=True)
+    torch.save(algo_dict(), path)
+    return path
+
+
+def gpu_tag(name: Optional[str] = None) -> str:
+    """"NVIDIA B200" -> "b200" (characters 7..10 of the device name, lower case)."""
+    if name is None:
+        name = torch.cuda.get_device_properties(0).name if torch.cuda.is_available() else "NVIDIA B200"
+    return name[7:11].lower().strip() or "gpu"
+
+
+def config_path(M: int, N: int, K: int, gpu: Optional[str] = None, directory: Optional[os.PathLike] = None) -> Path:
+    d = Path(directory) if directory else default_config_dir()
+    return d / f"m{M}n{N}k{K}_{gpu or gpu_tag()}.json"
+
+
+def bandwidth_path(comm_op: str, world_size: int, directory: Optional[os.PathLike] = None) -> Path:
+    d = Path(directory) if directory else default_config_dir()
+    return d / f"bandwidth_{comm_op}_tp{world_size}.pt"
+
+
+def load_config(path: os.PathLike) -> dict:
+    with open(path) as f:
+        return json.load(f)
+
+
+def save_stage1(path: os.PathLike, BMs: Sequence[int], BNs: Sequence[int], durs: Sequence[float],
+                algos: Sequence[int]) -> None:
+    Path(path).parent.mkdir(parents=True, exist_ok=True)
+    with open(path, "w") as f:
+        json.dump({"BM": list(BMs), "BN": list(BNs), "dur": list(durs), "Algo": list(algos)}, f, indent=4)
+
+
+def save_solution(path: os.PathLike, BM_: int, BN: int, dur: float, algo: int, hint: Sequence[int],
+                  cseg: Sequence[int], rldn: int = 1, **extra) -> None:
+    Path(path).parent.mkdir(parents=True, exist_ok=True)
+    data = {"BM": int(BM_), "BN": int(BN), "dur": float(dur), "Algo": int(algo),
+            "hint": [int(h) for h in hint], "cSeg": [int(c) for c in cseg], "rLDN": int(rldn)}
+    data.update(extra)
+    with open(path, "w") as f:
+        json.dump(data, f, indent=4)
+
+
+def is_tuned(cfg: dict) -> bool:
+    return "hint" in cfg and "cSeg" in cfg and not isinstance(cfg.get("Algo"), list)
+
+
+def default_solution(M: int, N: int, algo: int = 0, wave_size: int = 148, groups: Optional[List[int]] = None) -> dict:
+    """A usable config without any tuning run: analytic hint and one wave per group."""
+    from . import layout
+    p = algo_params(algo)
+    if N % p["BN"]:
+        algo = (algo & ~3) | 2
+        p = algo_params(algo)
+    tiles = (M // p["BM"]) * (N // p["BN"])
+    hint = layout.analytic_hint(M, N, p["BM"], p["BN"], p["raster"])
+    nw = layout.div_up(tiles, wave_size)
+    cseg = layout.cseg_from_wave_groups(tiles, wave_size, groups or [1] * nw)
+    return {"BM": p["BM"], "BN": p["BN"], "dur": 0.0, "Algo": algo, "hint": hint, "cSeg": cseg, "rLDN": 1}

@@ -1,0 +1,43 @@
+"""Config files and the Algo table (CPU)."""
+import json
+
+import torch
+
+from flashoverlap_b200.utils import config, layout
+
+
+def test_algo_table_matches_native(lib):
+    flat = list(torch.ops.flashoverlap_op.algo_table())
+    assert len(flat) == 5 * config.NUM_ALGOS
+    for a in range(config.NUM_ALGOS):
+        p = config.algo_params(a)
+        assert tuple(flat[5 * a:5 * a + 5]) == (p["BM"], p["BN"], p["BK"], p["stages"], p["raster"])
+
+
+def test_algo_dict_roundtrip(tmp_path):
+    d = config.algo_dict()
+    assert len(d) == config.NUM_ALGOS and all(len(k) == 12 for k in d)
+    path = config.save_algo_dict(tmp_path / "AlgoDict.pt")
+    assert torch.load(path, weights_only=False) == d
+
+
+def test_config_names_and_stages(tmp_path):
+    assert config.gpu_tag("NVIDIA B200") == "b200"
+    assert config.gpu_tag("NVIDIA A800-SXM4-80GB") == "a800"
+    p = config.config_path(4096, 8192, 8192, "b200", tmp_path)
+    assert p.name == "m4096n8192k8192_b200.json"
+    config.save_stage1(p, [128] * 10, [256] * 10, list(range(10)), list(range(10)))
+    c = config.load_config(p)
+    assert not config.is_tuned(c) and len(c["Algo"]) == 10
+    config.save_solution(p, 128, 256, 0.5, 4, [1, 0], [1, 1], tp=2, comm_op="all_reduce")
+    c = json.load(open(p))
+    assert config.is_tuned(c) and c["rLDN"] == 1 and c["hint"] == [1, 0] and c["cSeg"] == [1, 1] and c["tp"] == 2
+    assert config.bandwidth_path("all_reduce", 8, tmp_path).name == "bandwidth_all_reduce_tp8.pt"
+
+
+def test_default_solution_is_consistent():
+    c = config.default_solution(1024, 2048, algo=4)
+    tiles = (1024 // c["BM"]) * (2048 // c["BN"])
+    assert sorted(c["hint"]) == list(range(tiles)) and sum(c["cSeg"]) == tiles
+    c = config.default_solution(1024, 2048 + 128, algo=0)      # N not a multiple of 256 -> BN 128
+    assert c["BN"] == 128 and (c["Algo"] & 3) == 2

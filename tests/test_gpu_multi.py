@@ -1,0 +1,246 @@
+"""Multi-GPU tests: one process per GPU (NCCL), fused kernels over real NVLink peer memory.
+
+Skipped when fewer than two GPUs are visible; the same kernels' cross-rank protocol is covered
+on one GPU by the loopback tests in test_gpu_kernels.py.
+"""
+import os
+
+import pytest
+import torch
+import torch.distributed as dist
+
+from tests._mp import run_ranks
+
+pytestmark = pytest.mark.gpu
+
+
+def _world():
+    n = torch.cuda.device_count() if torch.cuda.is_available() else 0
+    if n < 2:
+        pytest.skip("needs at least 2 GPUs")
+    return 8 if n >= 8 else (4 if n >= 4 else 2)
+
+
+def _rand(shape, dev, seed, scale=0.5, dt=torch.bfloat16):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).to(dt).to(dev)
+
+
+def _setup(rank, world):
+    from flashoverlap_b200.parallel import bootstrap
+    impl = bootstrap.make_overlap_impl(rank, world)
+    impl.set_option("timeout_ms", 5000)
+    return impl
+
+
+def _fused_worker(rank, world):
+    from flashoverlap_b200 import ops
+    from flashoverlap_b200.utils import config, layout
+    dev = torch.device("cuda", rank)
+    impl = _setup(rank, world)
+    res = {}
+    for (M, N, K, algo) in ((1024, 2048, 512, 0), (2048, 1024, 256, 6)):
+        p = config.algo_params(algo)
+        BM, BN = p["BM"], p["BN"]
+        tiles = (M // BM) * (N // BN)
+        A, B = _rand((M, K), dev, 10 + rank), _rand((N, K), dev, 20 + rank)
+        ref = A.float() @ B.float().t()
+        dist.all_reduce(ref)
+        tol = 0.02 * ref.abs().max().item() + 1e-3
+        hint = layout.analytic_hint(M, N, BM, BN, p["raster"])
+        RA = layout.reorder_indices(tiles, hint, device=dev).reshape(M // BM, N // BN)
+        mm = torch.zeros(1, N // BN, device=dev, dtype=torch.int32)
+        e, eg = torch.empty(0, dtype=torch.int32), torch.empty(0, dtype=torch.int32, device=dev)
+        cseg = torch.tensor([tiles // 3, tiles - tiles // 3], dtype=torch.int32)
+        # all-reduce, reordered layout, symmetric output, per-tile flags; repeated calls
+        C = impl.symm_empty([M, N], "bfloat16")
+        for _ in range(3):
+            C.fill_(float("nan"))
+            torch.cuda.synchronize(); dist.barrier()
+            impl.gemm_allreduce_overlap(A, B, C, mm, RA, 1, e, eg, algo, False)
+        got = ops.unreorder(C, M, N, BM, BN, RA)
+        res[f"ar_reordered_{algo}"] = (got.float() - ref).abs().max().item() / tol
+        # wave groups + ordinary (non symmetric) output tensor
+        C2 = torch.full((M, N), float("nan"), device=dev, dtype=torch.bfloat16)
+        impl.gemm_allreduce_overlap(A, B, C2, mm, RA, 1, cseg, cseg.to(dev), algo, False)
+        res[f"ar_groups_{algo}"] = (ops.unreorder(C2, M, N, BM, BN, RA).float() - ref).abs().max().item() / tol
+        # natural layout
+        C.fill_(float("nan")); torch.cuda.synchronize(); dist.barrier()
+        impl.gemm_allreduce_fused(A, B, C, algo)
+        res[f"ar_natural_{algo}"] = (C.float() - ref).abs().max().item() / tol
+        # reduce-scatter, both ownership rules, both layouts
+        for strided in (1, 0):
+            impl.set_option("strided_rows", strided)
+            rows = layout.owned_rows(M, BM, world, rank, bool(strided)).to(dev)
+            D = torch.full((M // world, N), float("nan"), device=dev, dtype=torch.bfloat16)
+            impl.gemm_reducescatter_overlap(A, B, D, D, mm, RA, eg, 1, e, eg, algo, False)
+            got = ops.unreorder(D, M // world, N, BM // world, BN, RA)
+            res[f"rs_reordered_{algo}_{strided}"] = (got.float() - ref[rows]).abs().max().item() / tol
+            D.fill_(float("nan"))
+            impl.gemm_reducescatter_fused(A, B, D, algo)
+            res[f"rs_natural_{algo}_{strided}"] = (D.float() - ref[rows]).abs().max().item() / tol
+        impl.set_option("strided_rows", 1)
+    torch.cuda.synchronize()
+    res["status"] = impl.read_status()[0]
+    return res
+
+
+def test_fused_allreduce_reducescatter_multi_gpu(lib):
+    world = _world()
+    for r in run_ranks(_fused_worker, world, "nccl"):
+        assert r.pop("status") == 0
+        for k, v in r.items():
+            assert v <= 1.0, (k, v)
+
+
+def _api_worker(rank, world):
+    from flashoverlap_b200 import ops
+    from flashoverlap_b200.parallel import bootstrap
+    from flashoverlap_b200.utils import config, layout
+    dev = torch.device("cuda", rank)
+    impl = _setup(rank, world)
+    base = bootstrap.make_baseline_impl(rank, world)
+    res = {}
+    M, N, K, algo = 1024, 2048, 256, 0
+    p = config.algo_params(algo)
+    BM, BN = p["BM"], p["BN"]
+    tiles = (M // BM) * (N // BN)
+    A, B = _rand((M, K), dev, 30 + rank), _rand((N, K), dev, 40 + rank)
+    ref = A.float() @ B.float().t()
+    dist.all_reduce(ref)
+    tol = 0.03 * ref.abs().max().item() + 1e-3
+    C = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+    D = torch.empty(M // world, N, device=dev, dtype=torch.bfloat16)
+    # non-overlapped paths (natural layout, contiguous shards)
+    impl.gemm_allreduce(A, B, C, algo)
+    res["gemm_allreduce"] = (C.float() - ref).abs().max().item() / tol
+    impl.gemm_reducescatter(A, B, C, D, algo)
+    lo = rank * (M // world)
+    res["gemm_reducescatter"] = (D.float() - ref[lo:lo + M // world]).abs().max().item() / tol
+    base.gemm_allreduce(A, B, C)
+    res["baseline_allreduce"] = (C.float() - ref).abs().max().item() / tol
+    base.gemm_reducescatter(A, B, C, D)
+    res["baseline_reducescatter"] = (D.float() - ref[lo:lo + M // world]).abs().max().item() / tol
+    # bare collectives
+    x = torch.full((64, 256), float(rank + 1), device=dev, dtype=torch.bfloat16)
+    impl.nccl_allreduce(x)
+    res["nccl_allreduce"] = abs(x[0, 0].item() - world * (world + 1) / 2)
+    x.fill_(float(rank + 1))
+    impl.seg_allreduce(x, torch.tensor([1, 3], dtype=torch.int32), 4)
+    res["seg_allreduce"] = abs(x[-1, -1].item() - world * (world + 1) / 2)
+    x.fill_(1.0)
+    impl.nccl_reducescatter(x)
+    n = x.numel() // world
+    res["nccl_reducescatter"] = abs(x.view(-1)[rank * n].item() - world)
+    # counter-gated NCCL mechanism (the reference's scheme) on both collectives
+    impl.set_option("mode", 1)
+    wave = impl.get_option("sm_count") - impl.get_option("sm_margin")
+    hint = layout.analytic_hint(M, N, BM, BN, p["raster"])
+    cseg = layout.cseg_from_wave_groups(tiles, max(1, min(wave, tiles // 2)), [1] * layout.div_up(tiles, max(1, min(wave, tiles // 2))))
+    RA = layout.reorder_indices(tiles, hint, device=dev).reshape(M // BM, N // BN)
+    mm = torch.zeros(1, max(N // BN, len(cseg)), device=dev, dtype=torch.int32)
+    cseg_cpu = torch.tensor(cseg, dtype=torch.int32)
+    for _ in range(2):
+        C.fill_(float("nan"))
+        impl.gemm_allreduce_overlap(A, B, C, mm, RA, 1, cseg_cpu, cseg_cpu.to(dev), algo, False)
+    res["gated_allreduce"] = (ops.unreorder(C, M, N, BM, BN, RA).float() - ref).abs().max().item() / tol
+    RE = layout.generate_row_mapping(M, N, BM, BN, cseg, world, device=dev)
+    D.fill_(float("nan"))
+    impl.gemm_reducescatter_overlap(A, B, C, D, mm, RA, RE, 1, cseg_cpu, cseg_cpu.to(dev), algo, False)
+    got = ops.unreorder(D, M // world, N, BM // world, BN, RA)
+    res["gated_reducescatter"] = (got.float() - ref[rank::world]).abs().max().item() / tol
+    impl.set_option("mode", 0)
+    # variable-size all-to-all on packed rows vs torch
+    ml = torch.tensor([[(3 * i + 5 * j) % 7 + 1 for j in range(world)] for i in range(world)], dtype=torch.int32)
+    send_rows = int(sum(ml[rank, j] for j in range(world) if j != rank))
+    recv_rows = int(sum(ml[j, rank] for j in range(world) if j != rank))
+    src = _rand((send_rows, 128), dev, 50 + rank)
+    dst = torch.zeros(recv_rows, 128, device=dev, dtype=torch.bfloat16)
+    impl.nccl_all2all(src, dst, ml)
+    ins = [int(ml[rank, j]) if j != rank else 0 for j in range(world)]
+    outs = [int(ml[j, rank]) if j != rank else 0 for j in range(world)]
+    exp = torch.zeros_like(dst)
+    dist.all_to_all_single(exp, src, output_split_sizes=outs, input_split_sizes=ins)
+    res["nccl_all2all"] = (dst.float() - exp.float()).abs().max().item()
+    dst2 = torch.zeros_like(dst)
+    base.nccl_all2all(src, dst2, ml)
+    res["baseline_all2all"] = (dst2.float() - exp.float()).abs().max().item()
+    torch.cuda.synchronize()
+    res["status"] = impl.read_status()[0]
+    return res
+
+
+def test_reference_api_multi_gpu(lib):
+    world = _world()
+    for r in run_ranks(_api_worker, world, "nccl"):
+        assert r.pop("status") == 0
+        for k, v in r.items():
+            assert v <= 1.0, (k, v)
+
+
+def _layer_worker(rank, world):
+    from flashoverlap_b200.models import DecoderConfig, TPDecoderLayer
+    dev = torch.device("cuda", rank)
+    impl = _setup(rank, world)
+    cfg = DecoderConfig(hidden=1024, ffn=2048, n_heads=8, n_kv_heads=8 if world > 2 else 2, head_dim=128)
+    batch, seq = 2, 256
+    T = batch * seq
+    x_full = _rand((T, cfg.hidden), dev, 7, scale=1.0)
+    outs = {}
+    for mode in ("nccl", "fused"):
+        layer = TPDecoderLayer(cfg, rank, world, batch, seq, impl=mode, overlap_impl=impl, seed=3)
+        rows = layer.shard_rows().to(dev)
+        y = layer(x_full[rows])
+        full = torch.zeros(T, cfg.hidden, device=dev, dtype=torch.float32)
+        full[rows] = y.float()
+        dist.all_reduce(full)
+        outs[mode] = full
+    torch.cuda.synchronize()
+    err = (outs["nccl"] - outs["fused"]).abs().max().item()
+    return {"err": err, "scale": outs["nccl"].abs().max().item(), "status": impl.read_status()[0]}
+
+
+def test_decoder_layer_fused_matches_nccl(lib):
+    world = _world()
+    for r in run_ranks(_layer_worker, world, "nccl"):
+        assert r["status"] == 0
+        assert r["err"] <= 0.03 * r["scale"] + 1e-2, r
+
+
+def _timeout_worker(rank, world):
+    """Rank 1 never launches: rank 0's kernel must give up within its bound, report a status and
+    leave the context usable.  The failure is made on the host (a launch that does not happen)."""
+    import time
+    dev = torch.device("cuda", rank)
+    impl = _setup(rank, world)
+    impl.set_option("timeout_ms", 300)
+    M, N, K = 256, 512, 128
+    A, B = _rand((M, K), dev, 1), _rand((N, K), dev, 2)
+    C = impl.symm_empty([M, N], "bfloat16")
+    out = {"elapsed": 0.0, "status": [0] * 8}
+    torch.cuda.synchronize(); dist.barrier()
+    if rank == 0:
+        t = time.time()
+        impl.gemm_allreduce_fused(A, B, C, 0)
+        torch.cuda.synchronize()
+        out["elapsed"] = time.time() - t
+        out["status"] = impl.read_status()
+        try:
+            impl.check_status()
+            out["raised"] = False
+        except RuntimeError:
+            out["raised"] = True
+        out["alive"] = float(torch.ones(8, device=dev).sum().item())
+    dist.barrier()
+    return out
+
+
+def test_missing_peer_times_out_with_status(lib):
+    if (torch.cuda.device_count() if torch.cuda.is_available() else 0) < 2:
+        pytest.skip("needs at least 2 GPUs")
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    res = run_ranks(_timeout_worker, 2, "nccl")
+    r0 = res[0]
+    assert r0["status"][0] in (5, 6, 7), r0          # a cross-GPU wait gave up
+    assert r0["raised"] and r0["alive"] == 8.0
+    assert r0["elapsed"] < 10.0
