@@ -7,6 +7,7 @@
 #include <torch/custom_class.h>
 #include <torch/library.h>
 
+#include "common/fo_check.h"
 #include "comm/nccl_utils.h"
 #include "flags/fo_wait.h"
 #include "norm/fo_norm.h"
@@ -25,8 +26,8 @@ int sm_count_of_current_device() {
 }
 
 bool is_bf16(const at::Tensor& t, const char* name) {
-  TORCH_CHECK(t.is_cuda() && t.is_contiguous(), name, " must be a contiguous CUDA tensor");
-  TORCH_CHECK(t.scalar_type() == at::kBFloat16 || t.scalar_type() == at::kHalf, name,
+  FO_CHECK(t.is_cuda() && t.is_contiguous(), name, " must be a contiguous CUDA tensor");
+  FO_CHECK(t.scalar_type() == at::kBFloat16 || t.scalar_type() == at::kHalf, name,
               " must be bfloat16 or float16");
   return t.scalar_type() == at::kBFloat16;
 }
@@ -37,13 +38,13 @@ std::vector<int64_t> generate_nccl_id() { return fo::generate_nccl_id(); }
 void reorder_rmsnorm_eps(at::Tensor X, at::Tensor RX, at::Tensor RW, int64_t BM, int64_t BN,
                          int64_t rldn, at::Tensor RA, double eps) {
   const bool bf = is_bf16(X, "X");
-  TORCH_CHECK(RX.scalar_type() == X.scalar_type() && RW.scalar_type() == X.scalar_type(),
+  FO_CHECK(RX.scalar_type() == X.scalar_type() && RW.scalar_type() == X.scalar_type(),
               "X, RX and RW must share a dtype");
-  TORCH_CHECK(RX.dim() == 2 && RX.is_contiguous() && RX.is_cuda(), "RX must be [rows, dim]");
+  FO_CHECK(RX.dim() == 2 && RX.is_contiguous() && RX.is_cuda(), "RX must be [rows, dim]");
   const int rows = static_cast<int>(RX.size(0));
   const int dim = static_cast<int>(RX.size(1));
-  TORCH_CHECK(X.numel() >= RX.numel() && RW.numel() == dim, "shape mismatch");
-  TORCH_CHECK(RA.is_cuda() && RA.scalar_type() == at::kInt && RA.is_contiguous() &&
+  FO_CHECK(X.numel() >= RX.numel() && RW.numel() == dim, "shape mismatch");
+  FO_CHECK(RA.is_cuda() && RA.scalar_type() == at::kInt && RA.is_contiguous() &&
                   RA.numel() >= static_cast<int64_t>(rows / BM) * (dim / BN),
               "RA must be an int32 CUDA tensor with one entry per tile");
   c10::cuda::CUDAGuard guard(X.device());
@@ -63,13 +64,13 @@ void reorder_rmsnorm(at::Tensor X, at::Tensor RX, at::Tensor RW, int64_t BM, int
 
 void rmsnorm(at::Tensor X, at::Tensor RX, at::Tensor RW, double eps) {
   const bool bf = is_bf16(X, "X");
-  TORCH_CHECK(RX.scalar_type() == X.scalar_type() && RW.scalar_type() == X.scalar_type(),
+  FO_CHECK(RX.scalar_type() == X.scalar_type() && RW.scalar_type() == X.scalar_type(),
               "X, RX and RW must share a dtype");
-  TORCH_CHECK(X.dim() == 2 && RX.sizes() == X.sizes() && RX.is_contiguous() && RX.is_cuda(),
+  FO_CHECK(X.dim() == 2 && RX.sizes() == X.sizes() && RX.is_contiguous() && RX.is_cuda(),
               "X and RX must be [rows, dim]");
   const int rows = static_cast<int>(X.size(0));
   const int dim = static_cast<int>(X.size(1));
-  TORCH_CHECK(RW.numel() == dim, "RW must have dim elements");
+  FO_CHECK(RW.numel() == dim, "RW must have dim elements");
   c10::cuda::CUDAGuard guard(X.device());
   fo::cuda_check(fo::rmsnorm_launch(X.data_ptr(), RX.data_ptr(), RW.data_ptr(), rows, dim,
                                     static_cast<float>(eps), bf, sm_count_of_current_device(),
@@ -80,10 +81,10 @@ void rmsnorm(at::Tensor X, at::Tensor RX, at::Tensor RW, double eps) {
 void reorder_impl(at::Tensor X, at::Tensor Y, int64_t rows, int64_t dim, int64_t BM, int64_t BN,
                   int64_t rldn, at::Tensor RA, bool to_reordered) {
   is_bf16(X, "X");
-  TORCH_CHECK(Y.scalar_type() == X.scalar_type() && Y.is_cuda() && Y.is_contiguous(),
+  FO_CHECK(Y.scalar_type() == X.scalar_type() && Y.is_cuda() && Y.is_contiguous(),
               "Y must match X's dtype");
-  TORCH_CHECK(X.numel() == rows * dim && Y.numel() == rows * dim, "X and Y must hold rows*dim elements");
-  TORCH_CHECK(RA.is_cuda() && RA.scalar_type() == at::kInt && RA.is_contiguous() &&
+  FO_CHECK(X.numel() == rows * dim && Y.numel() == rows * dim, "X and Y must hold rows*dim elements");
+  FO_CHECK(RA.is_cuda() && RA.scalar_type() == at::kInt && RA.is_contiguous() &&
                   RA.numel() >= (rows / BM) * (dim / BN),
               "RA must be an int32 CUDA tensor with one entry per tile");
   c10::cuda::CUDAGuard guard(X.device());
@@ -97,22 +98,22 @@ void reorder_impl(at::Tensor X, at::Tensor Y, int64_t rows, int64_t dim, int64_t
 
 // Y (tile-contiguous) <- X (row-major [rows, dim]).
 void reorder(at::Tensor X, at::Tensor Y, int64_t BM, int64_t BN, int64_t rldn, at::Tensor RA) {
-  TORCH_CHECK(X.dim() == 2, "X must be [rows, dim]");
+  FO_CHECK(X.dim() == 2, "X must be [rows, dim]");
   reorder_impl(X, Y, X.size(0), X.size(1), BM, BN, rldn, RA, true);
 }
 
 // Y (row-major [rows, dim]) <- X (tile-contiguous).
 void unreorder(at::Tensor X, at::Tensor Y, int64_t BM, int64_t BN, int64_t rldn, at::Tensor RA) {
-  TORCH_CHECK(Y.dim() == 2, "Y must be [rows, dim]");
+  FO_CHECK(Y.dim() == 2, "Y must be [rows, dim]");
   reorder_impl(X, Y, Y.size(0), Y.size(1), BM, BN, rldn, RA, false);
 }
 
 // Bounded counting wait on MM[index] (see flags/fo_wait.h); status: int32[8] CUDA tensor.
 void wait_flag(int64_t target, at::Tensor MM, int64_t index, int64_t timeout_ms, at::Tensor status) {
-  TORCH_CHECK(MM.is_cuda() && MM.scalar_type() == at::kInt && MM.is_contiguous() &&
+  FO_CHECK(MM.is_cuda() && MM.scalar_type() == at::kInt && MM.is_contiguous() &&
                   index >= 0 && index < MM.numel(),
               "MM must be an int32 CUDA tensor and index in range");
-  TORCH_CHECK(status.is_cuda() && status.scalar_type() == at::kInt &&
+  FO_CHECK(status.is_cuda() && status.scalar_type() == at::kInt &&
                   status.numel() >= fo::kStatusWords,
               "status must be an int32 CUDA tensor with 8 words");
   c10::cuda::CUDAGuard guard(MM.device());
@@ -124,12 +125,12 @@ void wait_flag(int64_t target, at::Tensor MM, int64_t index, int64_t timeout_ms,
                  "wait_flag");
 }
 
-// Flattened Algo table: for each Algo index (BM, BN, BK, stages, raster strip width).
+// Flattened Algo table: for each Algo index (BM, BN, BK, stages, raster strip width, CTA pair).
 std::vector<int64_t> algo_table() {
   std::vector<int64_t> t;
   for (int a = 0; a < fo::kNumAlgos; ++a) {
     const fo::AlgoConfig c = fo::algo_config(a);
-    t.insert(t.end(), {c.bm, c.bn, c.bk, c.stages, c.raster_sw});
+    t.insert(t.end(), {c.bm, c.bn, c.bk, c.stages, c.raster_sw, c.cta2});
   }
   return t;
 }

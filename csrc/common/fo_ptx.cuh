@@ -1,5 +1,5 @@
 // Inline-PTX wrappers for the Blackwell (sm_100a) features used by the kernels in this
-// library: mbarrier, TMA tiled loads (never with cluster multicast), tcgen05 tensor-core
+// library: mbarrier, TMA tiled loads (each CTA fetches its own tiles), tcgen05 tensor-core
 // MMA with TMEM accumulators, scoped acquire/release flag accesses for cross-GPU
 // signalling, and bounded spin-waits that report a status instead of hanging.
 #pragma once
@@ -42,6 +42,31 @@ FO_DEVICE uint64_t globaltimer_ns() {
   uint64_t t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
+}
+
+// ------------------------------------------------------------------ thread-block clusters
+
+FO_DEVICE uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+FO_DEVICE void cluster_arrive_release() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+}
+FO_DEVICE void cluster_wait_acquire() {
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Address of the same shared-memory location in CTA `rank` of this cluster.
+FO_DEVICE uint32_t mapa_shared(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+// Arrive on an mbarrier that may live in another CTA of the cluster (address from mapa_shared).
+FO_DEVICE void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr)
+               : "memory");
 }
 
 // ------------------------------------------------------------------ mbarrier
@@ -99,7 +124,7 @@ FO_DEVICE bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, volatile int* a
   }
 }
 
-// ------------------------------------------------------------------ TMA (tiled, no multicast)
+// ------------------------------------------------------------------ TMA (tiled; one CTA per copy)
 
 FO_DEVICE void prefetch_tmap(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
@@ -118,6 +143,22 @@ FO_DEVICE void tma_load_2d(void* smem_dst, const CUtensorMap* m, uint64_t* bar, 
       : "memory");
 }
 
+// The same load issued by either CTA of a cta_group::2 pair: data lands in the issuing
+// CTA's shared memory, the byte count is credited to the barrier at the same offset in the
+// pair's leader CTA (bit 24 of a shared::cluster address selects the CTA of the pair).
+// Each CTA fetches its own operand slice; nothing is broadcast to the peer.
+constexpr uint32_t kPeerBitMask = 0xFEFFFFFFu;
+FO_DEVICE void tma_load_2d_pair(void* smem_dst, const CUtensorMap* m, uint64_t* bar, int32_t c0,
+                                int32_t c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4}], [%2];"
+      :
+      : "r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)),
+        "r"(smem_u32(bar) & kPeerBitMask), "r"(c0), "r"(c1)
+      : "memory");
+}
+
 // ------------------------------------------------------------------ tcgen05 / TMEM
 
 FO_DEVICE void tmem_alloc(uint32_t* smem_dst, uint32_t ncols) {  // whole warp
@@ -131,6 +172,20 @@ FO_DEVICE void tmem_relinquish() {  // whole warp
 }
 FO_DEVICE void tmem_dealloc(uint32_t taddr, uint32_t ncols) {  // whole warp
   asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols)
+               : "memory");
+}
+
+FO_DEVICE void tmem_alloc_pair(uint32_t* smem_dst, uint32_t ncols) {  // same warp id in both CTAs
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                   smem_u32(smem_dst)),
+               "r"(ncols)
+               : "memory");
+}
+FO_DEVICE void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+FO_DEVICE void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols)
                : "memory");
 }
 
@@ -175,6 +230,32 @@ FO_DEVICE void umma_f16_ss(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, ui
       "}\n"
       :
       : "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// Pair form: one thread of the leader CTA issues; the two SMs each compute their 128 rows of
+// a 256-row tile, A rows and B columns are read from both CTAs' shared memory.
+FO_DEVICE void umma_f16_ss_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
+      "}\n"
+      :
+      : "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// Arrive (once the pair's MMAs issued so far have completed) on the barrier at this offset in
+// every CTA of the cluster selected by `cta_mask`.  This multicast is a barrier signal, not a
+// data load.
+FO_DEVICE void umma_commit_pair(uint64_t* bar, uint16_t cta_mask) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 "
+      "[%0], %1;" ::"r"(smem_u32(bar)),
+      "h"(cta_mask)
       : "memory");
 }
 

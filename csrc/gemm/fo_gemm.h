@@ -30,4 +30,9 @@ cudaError_t launch_gemm(int algo, bool bf16, bool fused, const GemmTensorMaps& m
 
 int gemm_smem_bytes(int algo);
 
+// Largest grid (CTAs per virtual rank) of this Algo's kernel that is co-resident on the
+// current device: one CTA per SM, or two per schedulable cluster for the CTA-pair kernels.
+// Fused launches must not exceed it, since their CTAs wait for the same CTAs on the peers.
+int gemm_max_resident_ctas(int algo, bool bf16, bool fused);
+
 }  // namespace fo

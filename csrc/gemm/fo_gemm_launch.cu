@@ -27,11 +27,12 @@ EncodeFn get_encode_fn() {
   return fn;
 }
 
-template <int BN, int STAGES, bool BF16, bool FUSED>
-cudaError_t launch_one(const GemmTensorMaps& maps, const GemmParams& p, int grid_x, int nvr,
-                       bool cooperative, cudaStream_t stream) {
-  auto kernel = fo_gemm_kernel<BN, STAGES, BF16, FUSED>;
-  constexpr int smem = GemmSmem<BN, STAGES>::kTotalBytes;
+// query != nullptr: do not launch, report the largest co-resident grid instead.
+template <int BN, int STAGES, bool BF16, bool FUSED, bool CTA2>
+cudaError_t launch_one(const GemmTensorMaps* maps, const GemmParams* p, int grid_x, int nvr,
+                       bool cooperative, cudaStream_t stream, int* query) {
+  auto kernel = fo_gemm_kernel<BN, STAGES, BF16, FUSED, CTA2>;
+  constexpr int smem = GemmSmem<BN, STAGES, CTA2>::kTotalBytes;
   static bool attr_set[16] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -41,30 +42,65 @@ cudaError_t launch_one(const GemmTensorMaps& maps, const GemmParams& p, int grid
     attr_set[dev] = true;
   }
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(grid_x, nvr, 1);
   cfg.blockDim = dim3(FUSED ? kThreadsFused : kThreadsPlain, 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
+  cfg.attrs = attr;
   cfg.numAttrs = 0;
-  if (cooperative) {
-    attr[0].id = cudaLaunchAttributeCooperative;
-    attr[0].val.cooperative = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
+  if (CTA2) {
+    attr[cfg.numAttrs].id = cudaLaunchAttributeClusterDimension;
+    attr[cfg.numAttrs].val.clusterDim.x = 2;
+    attr[cfg.numAttrs].val.clusterDim.y = 1;
+    attr[cfg.numAttrs].val.clusterDim.z = 1;
+    ++cfg.numAttrs;
   }
-  return cudaLaunchKernelEx(&cfg, kernel, maps, p);
+  if (query != nullptr) {
+    cudaDeviceProp prop;
+    cudaError_t e = cudaGetDeviceProperties(&prop, dev);
+    if (e != cudaSuccess) return e;
+    if (!CTA2) {
+      *query = prop.multiProcessorCount;  // shared memory admits exactly one CTA per SM
+      return cudaSuccess;
+    }
+    cfg.gridDim = dim3(prop.multiProcessorCount & ~1, 1, 1);
+    int clusters = 0;
+    e = cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg);
+    if (e != cudaSuccess) return e;
+    *query = 2 * clusters;
+    return cudaSuccess;
+  }
+  if (CTA2) grid_x &= ~1;
+  if (grid_x < (CTA2 ? 2 : 1)) grid_x = CTA2 ? 2 : 1;
+  cfg.gridDim = dim3(grid_x, nvr, 1);
+  if (cooperative) {
+    attr[cfg.numAttrs].id = cudaLaunchAttributeCooperative;
+    attr[cfg.numAttrs].val.cooperative = 1;
+    ++cfg.numAttrs;
+  }
+  return cudaLaunchKernelEx(&cfg, kernel, *maps, *p);
 }
 
 template <bool BF16, bool FUSED>
-cudaError_t launch_kernel_index(int kidx, const GemmTensorMaps& maps, const GemmParams& p,
-                                int grid_x, int nvr, bool coop, cudaStream_t s) {
+cudaError_t launch_kernel_index(int kidx, const GemmTensorMaps* maps, const GemmParams* p,
+                                int grid_x, int nvr, bool coop, cudaStream_t s, int* query) {
   switch (kidx) {
-    case 0: return launch_one<256, 4, BF16, FUSED>(maps, p, grid_x, nvr, coop, s);
-    case 1: return launch_one<256, 3, BF16, FUSED>(maps, p, grid_x, nvr, coop, s);
-    case 2: return launch_one<128, 6, BF16, FUSED>(maps, p, grid_x, nvr, coop, s);
-    default: return launch_one<128, 4, BF16, FUSED>(maps, p, grid_x, nvr, coop, s);
+    case 0: return launch_one<256, 4, BF16, FUSED, false>(maps, p, grid_x, nvr, coop, s, query);
+    case 1: return launch_one<256, 6, BF16, FUSED, true>(maps, p, grid_x, nvr, coop, s, query);
+    case 2: return launch_one<128, 6, BF16, FUSED, false>(maps, p, grid_x, nvr, coop, s, query);
+    default: return launch_one<128, 4, BF16, FUSED, false>(maps, p, grid_x, nvr, coop, s, query);
   }
+}
+
+cudaError_t dispatch(int algo, bool bf16, bool fused, const GemmTensorMaps* maps, const GemmParams* p,
+                     int grid_x, int nvr, bool coop, cudaStream_t s, int* query) {
+  const int kidx = algo & 3;
+  if (bf16) {
+    if (fused) return launch_kernel_index<true, true>(kidx, maps, p, grid_x, nvr, coop, s, query);
+    return launch_kernel_index<true, false>(kidx, maps, p, grid_x, nvr, coop, s, query);
+  }
+  if (fused) return launch_kernel_index<false, true>(kidx, maps, p, grid_x, nvr, coop, s, query);
+  return launch_kernel_index<false, false>(kidx, maps, p, grid_x, nvr, coop, s, query);
 }
 
 }  // namespace
@@ -91,6 +127,7 @@ std::string prepare_tiling(int algo, GemmParams* p) {
   if (algo < 0 || algo >= kNumAlgos) return "Algo index out of range";
   const AlgoConfig c = algo_config(algo);
   if (p->M % c.bm != 0) return "M must be a multiple of 128";
+  if (c.cta2 && p->M % (2 * c.bm) != 0) return "M must be a multiple of 256 for a CTA-pair Algo";
   if (p->N % c.bn != 0) return "N must be a multiple of the tile width BN of this Algo";
   if (p->K % 8 != 0) return "K must be a multiple of 8";
   p->tiles_m = p->M / c.bm;
@@ -104,23 +141,35 @@ std::string prepare_tiling(int algo, GemmParams* p) {
 
 int gemm_smem_bytes(int algo) {
   switch (algo & 3) {
-    case 0: return GemmSmem<256, 4>::kTotalBytes;
-    case 1: return GemmSmem<256, 3>::kTotalBytes;
-    case 2: return GemmSmem<128, 6>::kTotalBytes;
-    default: return GemmSmem<128, 4>::kTotalBytes;
+    case 0: return GemmSmem<256, 4, false>::kTotalBytes;
+    case 1: return GemmSmem<256, 6, true>::kTotalBytes;
+    case 2: return GemmSmem<128, 6, false>::kTotalBytes;
+    default: return GemmSmem<128, 4, false>::kTotalBytes;
   }
+}
+
+int gemm_max_resident_ctas(int algo, bool bf16, bool fused) {
+  static int cache[16][4][2][2] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 16) dev = 0;
+  int& slot = cache[dev][algo & 3][bf16 ? 1 : 0][fused ? 1 : 0];
+  if (slot == 0) {
+    int q = 0;
+    if (dispatch(algo, bf16, fused, nullptr, nullptr, 0, 1, false, nullptr, &q) != cudaSuccess || q <= 0) {
+      cudaGetLastError();
+      q = 2;  // conservative: a single CTA pair
+    }
+    slot = q;
+  }
+  return slot;
 }
 
 cudaError_t launch_gemm(int algo, bool bf16, bool fused, const GemmTensorMaps& maps,
                         const GemmParams& p, int grid_x, int nvr, bool cooperative,
                         cudaStream_t stream) {
-  const int kidx = algo & 3;
-  if (bf16) {
-    if (fused) return launch_kernel_index<true, true>(kidx, maps, p, grid_x, nvr, cooperative, stream);
-    return launch_kernel_index<true, false>(kidx, maps, p, grid_x, nvr, cooperative, stream);
-  }
-  if (fused) return launch_kernel_index<false, true>(kidx, maps, p, grid_x, nvr, cooperative, stream);
-  return launch_kernel_index<false, false>(kidx, maps, p, grid_x, nvr, cooperative, stream);
+  if (algo_config(algo).cta2 && (cooperative || nvr != 1)) return cudaErrorInvalidConfiguration;
+  return dispatch(algo, bf16, fused, &maps, &p, grid_x, nvr, cooperative, stream, nullptr);
 }
 
 }  // namespace fo

@@ -2,7 +2,7 @@
 // configurations ("Algo" indices) that the JSON configs and the tuner refer to.
 // The reference indexes 102 CUTLASS instantiations by an integer Algo
 // (src/tiling/gemm_dispatcher.h:7-27, tool/generate_instances.py:5-45); here an Algo names a
-// (BN, pipeline depth, raster strip width) triple of one hand-written kernel.
+// (BN, pipeline depth, CTA-pair mode, raster strip width) tuple of one hand-written kernel.
 #pragma once
 #include <cuda.h>
 #include <cstdint>
@@ -72,6 +72,7 @@ struct AlgoConfig {
   int bm, bn, bk;
   int stages;
   int raster_sw;  // 0 => full row panels (strip = all N tiles)
+  int cta2;       // 1: CTA pairs share 256-row tiles through tcgen05.mma.cta_group::2
 };
 
 constexpr int kNumAlgos = 24;
@@ -79,7 +80,8 @@ constexpr int kNumAlgos = 24;
 inline AlgoConfig algo_config(int algo) {
   // algo = raster index * 4 + kernel index
   static const int kKernelBN[4] = {256, 256, 128, 128};
-  static const int kKernelStages[4] = {4, 3, 6, 4};
+  static const int kKernelStages[4] = {4, 6, 6, 4};
+  static const int kKernelCta2[4] = {0, 1, 0, 0};
   static const int kRaster[6] = {8, 4, 2, 1, 16, 0};
   if (algo < 0 || algo >= kNumAlgos) algo = 0;
   AlgoConfig c;
@@ -88,6 +90,7 @@ inline AlgoConfig algo_config(int algo) {
   c.bn = kKernelBN[algo & 3];
   c.stages = kKernelStages[algo & 3];
   c.raster_sw = kRaster[algo >> 2];
+  c.cta2 = kKernelCta2[algo & 3];
   return c;
 }
 

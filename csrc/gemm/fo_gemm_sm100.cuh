@@ -13,7 +13,7 @@
 //                reference's GEMM + wait kernel + NCCL call (src/overlap_impl.cu:214-321).
 //
 // Roles inside a CTA (one CTA per SM, 128 x BN output tiles, BK = 64):
-//   warp 0      TMA producer: 2-D tiled loads (128-byte swizzle, no multicast) into a
+//   warp 0      TMA producer: 2-D tiled loads (128-byte swizzle, one CTA per copy) into a
 //               STAGES-deep shared-memory ring, completion counted on mbarriers;
 //   warp 1      MMA issuer: one thread issues tcgen05.mma.kind::f16 (fp32 accumulate in TMEM),
 //               tcgen05.commit releases ring slots and publishes finished accumulators;
@@ -22,6 +22,12 @@
 //               128-byte coalesced global (local or peer) stores, then the signal;
 //   warps 6-9   (fused only) reducer for the row slices this rank owns.
 // The two TMEM accumulators let tile i's epilogue run under tile i+1's main loop.
+//
+// CTA2 variant: two CTAs of a cluster (adjacent SMs) share one 256 x 256 tile through
+// tcgen05.mma.cta_group::2.  Each CTA loads its own 128 rows of A and its own 128 of the 256
+// rows of B, the leader CTA's MMA thread issues for both, and each CTA ends up with the
+// accumulators of its own 128 x 256 half, so epilogue, signalling and reducer are unchanged.
+// Halving the B traffic per SM is what lifts the kernel to library-GEMM throughput.
 //
 // Every wait is bounded: on expiry the role records a status code, raises a CTA-wide abort
 // flag, the producer drains its TMA loads in flight, TMEM is freed and the kernel returns.
@@ -35,10 +41,11 @@
 
 namespace fo {
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, bool CTA2 = false>
 struct GemmSmem {
   static constexpr int kABytes = kBM * kBK * 2;
-  static constexpr int kBBytes = BN * kBK * 2;
+  static constexpr int kBRows = CTA2 ? BN / 2 : BN;  // B rows this CTA loads per k-block
+  static constexpr int kBBytes = kBRows * kBK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kEpiBufBytes = kBM * 128;  // 128 rows x 64 16-bit columns
   static constexpr int kRingBytes = STAGES * kStageBytes;
@@ -117,11 +124,11 @@ constexpr int kReducerThreads = 128;
 constexpr int kThreadsPlain = 64 + kEpilogueThreads;
 constexpr int kThreadsFused = kThreadsPlain + kReducerThreads;
 
-template <int BN, int STAGES, bool BF16, bool FUSED>
+template <int BN, int STAGES, bool BF16, bool FUSED, bool CTA2>
 __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
     fo_gemm_kernel(const __grid_constant__ GemmTensorMaps maps,
                    const __grid_constant__ GemmParams p) {
-  using L = GemmSmem<BN, STAGES>;
+  using L = GemmSmem<BN, STAGES, CTA2>;
   extern __shared__ uint8_t smem_raw[];
   // The ring must start on a 1024-byte boundary of the shared window.
   const uint32_t raw_addr = ptx::smem_u32(smem_raw);
@@ -146,6 +153,18 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
   const int me = p.rank_base + vr;     // rank this CTA acts as
   const int num_kb = (p.K + kBK - 1) / kBK;
   constexpr uint32_t kTmemCols = 2 * BN;
+  // Scheduling unit: a CTA (128-row tiles) or a CTA pair (256-row tiles, this CTA's half).
+  const uint32_t cta_rank = CTA2 ? ptx::cluster_ctarank() : 0u;
+  const bool leader = cta_rank == 0u;
+  const int unit = CTA2 ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+  const int num_units = CTA2 ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
+  const int sched_tiles_m = CTA2 ? p.tiles_m / 2 : p.tiles_m;
+  const int sched_tiles = sched_tiles_m * p.tiles_n;
+  auto my_tile = [&](int pos) {
+    TileCoord tc = tile_of_position(pos, sched_tiles_m, p.tiles_n, p.raster_sw);
+    if (CTA2) tc.m = 2 * tc.m + static_cast<int>(cta_rank);
+    return tc;
+  };
   int32_t* status = p.status[vr];
   // Pipeline waits inside the CTA can legitimately last as long as a cross-GPU wait that
   // another role is sitting in, so their bound is a multiple of it.
@@ -158,7 +177,8 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
     }
     for (int i = 0; i < 2; ++i) {
       ptx::mbar_init(&tmem_full_bar[i], 1);
-      ptx::mbar_init(&tmem_empty_bar[i], kEpilogueThreads);
+      // one arrival per epilogue warp, from both CTAs of a pair
+      ptx::mbar_init(&tmem_empty_bar[i], CTA2 ? 8 : 4);
     }
     *s_abort = 0;
     *s_ep_ok = 1;
@@ -172,11 +192,22 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
     ptx::prefetch_tmap(&maps.b[vr]);
   }
   if (warp_idx == 1) {
-    ptx::tmem_alloc(s_tmem_base, kTmemCols);
-    ptx::tmem_relinquish();
+    if constexpr (CTA2) {
+      ptx::tmem_alloc_pair(s_tmem_base, kTmemCols);
+      ptx::tmem_relinquish_pair();
+    } else {
+      ptx::tmem_alloc(s_tmem_base, kTmemCols);
+      ptx::tmem_relinquish();
+    }
   }
   ptx::tc_fence_before_sync();
-  __syncthreads();
+  if constexpr (CTA2) {
+    // Both CTAs' barriers must be initialised before either receives a remote signal.
+    ptx::cluster_arrive_release();
+    ptx::cluster_wait_acquire();
+  } else {
+    __syncthreads();
+  }
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = *s_tmem_base;
 
@@ -187,8 +218,8 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
       uint32_t phase = 0;
       uint32_t issued = 0;
       bool ok = true;
-      for (int pos = blockIdx.x; ok && pos < p.num_tiles; pos += gridDim.x) {
-        const TileCoord tc = tile_of_position(pos, p.tiles_m, p.tiles_n, p.raster_sw);
+      for (int pos = unit; ok && pos < sched_tiles; pos += num_units) {
+        const TileCoord tc = my_tile(pos);
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!ptx::mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, s_abort, pipe_timeout)) {
             ptx::report_status(status, kStatusTimeoutSmemEmpty, pos, kb, stage);
@@ -198,9 +229,17 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
           }
           uint8_t* sa = smem + stage * L::kStageBytes;
           uint8_t* sb = sa + L::kABytes;
-          ptx::mbar_arrive_expect_tx(&full_bar[stage], L::kStageBytes);
-          ptx::tma_load_2d(sa, &maps.a[vr], &full_bar[stage], kb * kBK, tc.m * kBM);
-          ptx::tma_load_2d(sb, &maps.b[vr], &full_bar[stage], kb * kBK, tc.n * BN);
+          if constexpr (CTA2) {
+            // The leader's barrier collects the bytes of both CTAs.
+            if (leader) ptx::mbar_arrive_expect_tx(&full_bar[stage], 2 * L::kStageBytes);
+            ptx::tma_load_2d_pair(sa, &maps.a[vr], &full_bar[stage], kb * kBK, tc.m * kBM);
+            ptx::tma_load_2d_pair(sb, &maps.b[vr], &full_bar[stage], kb * kBK,
+                                  tc.n * BN + static_cast<int>(cta_rank) * L::kBRows);
+          } else {
+            ptx::mbar_arrive_expect_tx(&full_bar[stage], L::kStageBytes);
+            ptx::tma_load_2d(sa, &maps.a[vr], &full_bar[stage], kb * kBK, tc.m * kBM);
+            ptx::tma_load_2d(sb, &maps.b[vr], &full_bar[stage], kb * kBK, tc.n * BN);
+          }
           ++issued;
           if (++stage == STAGES) {
             stage = 0;
@@ -210,7 +249,10 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
       }
       // Drain: do not leave the CTA while a bulk copy may still write its shared memory.
       // For each ring slot wait (bounded) for the last load issued into it.
-      for (int s = 0; s < STAGES; ++s) {
+      // (In a pair the follower's loads are counted on the leader's barriers, which the
+      // follower cannot poll; it relies on the cluster-wide barrier at the end instead: the
+      // leader reaches it only after draining the barriers that count both CTAs' bytes.)
+      for (int s = 0; s < STAGES && (!CTA2 || leader); ++s) {
         if (issued <= static_cast<uint32_t>(s)) continue;
         const uint32_t last = ((issued - 1 - s) / STAGES) * STAGES + s;  // last issue index on slot s
         const uint32_t par = (last / STAGES) & 1u;
@@ -221,14 +263,14 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
     }
   } else if (warp_idx == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      constexpr uint32_t idesc = ptx::make_idesc_f16(BF16, kBM, BN);
+    if (lane == 0 && leader) {
+      constexpr uint32_t idesc = ptx::make_idesc_f16(BF16, CTA2 ? 2 * kBM : kBM, BN);
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int pos = blockIdx.x; ok && pos < p.num_tiles; pos += gridDim.x) {
+      for (int pos = unit; ok && pos < sched_tiles; pos += num_units) {
         if (!ptx::mbar_wait_bounded(&tmem_empty_bar[acc], acc_phase ^ 1u, s_abort, pipe_timeout)) {
           ptx::report_status(status, kStatusTimeoutTmemEmpty, pos, acc, 0);
           *s_abort = 1;
@@ -250,18 +292,33 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
 #pragma unroll
           for (int k = 0; k < kBK / 16; ++k) {
             // advance 16 elements (32 B) along K inside the swizzle atom: +2 in 16-byte units
-            ptx::umma_f16_ss(tmem_d, da + static_cast<uint64_t>(2 * k),
-                             db + static_cast<uint64_t>(2 * k), idesc,
-                             (kb > 0 || k > 0) ? 1u : 0u);
+            if constexpr (CTA2) {
+              ptx::umma_f16_ss_pair(tmem_d, da + static_cast<uint64_t>(2 * k),
+                                    db + static_cast<uint64_t>(2 * k), idesc,
+                                    (kb > 0 || k > 0) ? 1u : 0u);
+            } else {
+              ptx::umma_f16_ss(tmem_d, da + static_cast<uint64_t>(2 * k),
+                               db + static_cast<uint64_t>(2 * k), idesc,
+                               (kb > 0 || k > 0) ? 1u : 0u);
+            }
           }
-          ptx::umma_commit(&empty_bar[stage]);  // slot reusable once these MMAs have read it
+          // slot reusable (in both CTAs of a pair) once these MMAs have read it
+          if constexpr (CTA2) {
+            ptx::umma_commit_pair(&empty_bar[stage], 3);
+          } else {
+            ptx::umma_commit(&empty_bar[stage]);
+          }
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1u;
           }
         }
         if (!ok) break;
-        ptx::umma_commit(&tmem_full_bar[acc]);  // accumulator complete
+        if constexpr (CTA2) {
+          ptx::umma_commit_pair(&tmem_full_bar[acc], 3);  // accumulators complete in both CTAs
+        } else {
+          ptx::umma_commit(&tmem_full_bar[acc]);
+        }
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1u;
       }
@@ -278,8 +335,12 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
     uint32_t acc_phase = 0;
     bool first_push = true;
 
-    for (int pos = blockIdx.x; pos < p.num_tiles; pos += gridDim.x) {
-      const TileCoord tc = tile_of_position(pos, p.tiles_m, p.tiles_n, p.raster_sw);
+    // tmem_empty lives in the leader CTA of a pair
+    const uint32_t tmem_empty_addr0 =
+        CTA2 ? ptx::mapa_shared(ptx::smem_u32(&tmem_empty_bar[0]), 0u) : ptx::smem_u32(&tmem_empty_bar[0]);
+
+    for (int pos = unit; pos < sched_tiles; pos += num_units) {
+      const TileCoord tc = my_tile(pos);
       const int t = tc.m * p.tiles_n + tc.n;
       const int r = (p.RA != nullptr) ? p.RA[t] : t;
 
@@ -344,9 +405,10 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
         ptx::tmem_ld_32x32b_x32(t_row + c * 64 + 32, v1);
         ptx::tmem_ld_wait();
         if (c == BN / 64 - 1) {
-          // Accumulator fully read: hand it back to the MMA warp.
+          // Accumulator fully read by this warp: hand it back to the (leader's) MMA warp.
           ptx::tc_fence_before_sync();
-          ptx::mbar_arrive(&tmem_empty_bar[acc]);
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive_cluster(tmem_empty_addr0 + static_cast<uint32_t>(acc) * 8u);
         }
         uint8_t* buf = epi + (c & 1) * L::kEpiBufBytes + my_row * 128;
 #pragma unroll
@@ -422,8 +484,8 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
       const uint8_t* stage_me = reinterpret_cast<const uint8_t*>(p.stage[me]);
 
       int slot = 0;
-      for (int pos = blockIdx.x; pos < p.num_tiles; pos += gridDim.x, slot ^= 1) {
-        const TileCoord tc = tile_of_position(pos, p.tiles_m, p.tiles_n, p.raster_sw);
+      for (int pos = unit; pos < sched_tiles; pos += num_units, slot ^= 1) {
+        const TileCoord tc = my_tile(pos);
         const int t = tc.m * p.tiles_n + tc.n;
         const int r = (p.RA != nullptr) ? p.RA[t] : t;
         if (rt == 0) {
@@ -532,10 +594,21 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
   }
 
   ptx::tc_fence_before_sync();
-  __syncthreads();
-  if (warp_idx == 1) {
-    ptx::tc_fence_after_sync();
-    ptx::tmem_dealloc(tmem_base, kTmemCols);
+  if constexpr (CTA2) {
+    // Neither CTA may free TMEM or leave while the other can still signal its barriers or
+    // its MMAs read this CTA's shared memory.
+    ptx::cluster_arrive_release();
+    ptx::cluster_wait_acquire();
+    if (warp_idx == 1) {
+      ptx::tc_fence_after_sync();
+      ptx::tmem_dealloc_pair(tmem_base, kTmemCols);
+    }
+  } else {
+    __syncthreads();
+    if (warp_idx == 1) {
+      ptx::tc_fence_after_sync();
+      ptx::tmem_dealloc(tmem_base, kTmemCols);
+    }
   }
 }
 

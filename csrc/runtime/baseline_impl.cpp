@@ -12,7 +12,8 @@ ncclDataType_t nccl_dtype(const at::Tensor& t) {
   if (t.scalar_type() == at::kBFloat16) return ncclBfloat16;
   if (t.scalar_type() == at::kHalf) return ncclFloat16;
   if (t.scalar_type() == at::kFloat) return ncclFloat32;
-  TORCH_CHECK(false, "unsupported dtype for a collective");
+  FO_CHECK(false, "unsupported dtype for a collective");
+  return ncclFloat16;
 }
 }  // namespace
 
@@ -25,8 +26,8 @@ BaselineImpl::~BaselineImpl() {
 cudaStream_t BaselineImpl::stream() const { return c10::cuda::getCurrentCUDAStream().stream(); }
 
 void BaselineImpl::NcclInit(int64_t rank, int64_t world, std::vector<int64_t> id) {
-  TORCH_CHECK(world >= 1 && rank >= 0 && rank < world, "bad rank/world");
-  TORCH_CHECK(comm_ == nullptr, "nccl_init was already called");
+  FO_CHECK(world >= 1 && rank >= 0 && rank < world, "bad rank/world");
+  FO_CHECK(comm_ == nullptr, "nccl_init was already called");
   rank_ = static_cast<int>(rank);
   world_ = static_cast<int>(world);
   if (world_ > 1) {
@@ -63,7 +64,7 @@ void BaselineImpl::NcclReduceScatter(at::Tensor C) {
 
 void BaselineImpl::NcclAll2All(at::Tensor C, at::Tensor D, at::Tensor mLen_CPU) {
   if (world_ == 1) return;
-  TORCH_CHECK(!mLen_CPU.is_cuda() && mLen_CPU.scalar_type() == at::kInt &&
+  FO_CHECK(!mLen_CPU.is_cuda() && mLen_CPU.scalar_type() == at::kInt &&
                   mLen_CPU.numel() == static_cast<int64_t>(world_) * world_,
               "mLen_CPU must be an int32 host tensor of shape [world, world]");
   const int* ml = mLen_CPU.data_ptr<int>();

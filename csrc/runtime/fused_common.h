@@ -8,6 +8,7 @@
 #include <string>
 
 #include "../comm/symmetric_heap.h"
+#include "../common/fo_check.h"
 #include "../common/fo_status.h"
 #include "../gemm/fo_gemm.h"
 
@@ -22,7 +23,7 @@ constexpr size_t kSignalMaxFlags = 65536;
 constexpr size_t kSignalBytes = kSignalFlagsOffset + kSignalMaxFlags * sizeof(uint32_t);
 
 inline void cuda_check(cudaError_t e, const char* what) {
-  TORCH_CHECK(e == cudaSuccess, "CUDA failure in ", what, ": ", cudaGetErrorString(e));
+  FO_CHECK(e == cudaSuccess, "CUDA failure in ", what, ": ", cudaGetErrorString(e));
 }
 
 struct GemmShape {
@@ -32,13 +33,13 @@ struct GemmShape {
 
 // A [M,K], B [N,K] (weight layout), both contiguous, same 16-bit floating type.
 inline GemmShape check_operands(const at::Tensor& A, const at::Tensor& B) {
-  TORCH_CHECK(A.is_cuda() && B.is_cuda(), "A and B must be CUDA tensors");
-  TORCH_CHECK(A.dim() == 2 && B.dim() == 2, "A must be [M,K] and B must be [N,K]");
-  TORCH_CHECK(A.is_contiguous() && B.is_contiguous(), "A and B must be contiguous");
-  TORCH_CHECK(A.scalar_type() == B.scalar_type(), "A and B must have the same dtype");
-  TORCH_CHECK(A.scalar_type() == at::kBFloat16 || A.scalar_type() == at::kHalf,
+  FO_CHECK(A.is_cuda() && B.is_cuda(), "A and B must be CUDA tensors");
+  FO_CHECK(A.dim() == 2 && B.dim() == 2, "A must be [M,K] and B must be [N,K]");
+  FO_CHECK(A.is_contiguous() && B.is_contiguous(), "A and B must be contiguous");
+  FO_CHECK(A.scalar_type() == B.scalar_type(), "A and B must have the same dtype");
+  FO_CHECK(A.scalar_type() == at::kBFloat16 || A.scalar_type() == at::kHalf,
               "only bfloat16 and float16 operands are supported");
-  TORCH_CHECK(A.size(1) == B.size(1), "A [M,K] and B [N,K] disagree on K");
+  FO_CHECK(A.size(1) == B.size(1), "A [M,K] and B [N,K] disagree on K");
   GemmShape s;
   s.M = static_cast<int>(A.size(0));
   s.K = static_cast<int>(A.size(1));
@@ -48,14 +49,14 @@ inline GemmShape check_operands(const at::Tensor& A, const at::Tensor& B) {
 }
 
 inline void check_out(const at::Tensor& C, const at::Tensor& A, int64_t numel, const char* name) {
-  TORCH_CHECK(C.is_cuda() && C.is_contiguous(), name, " must be a contiguous CUDA tensor");
-  TORCH_CHECK(C.scalar_type() == A.scalar_type(), name, " must have the operands' dtype");
-  TORCH_CHECK(C.numel() >= numel, name, " is too small: needs ", numel, " elements");
+  FO_CHECK(C.is_cuda() && C.is_contiguous(), name, " must be a contiguous CUDA tensor");
+  FO_CHECK(C.scalar_type() == A.scalar_type(), name, " must have the operands' dtype");
+  FO_CHECK(C.numel() >= numel, name, " is too small: needs ", numel, " elements");
 }
 
 inline const int* int_ptr_or_null(const at::Tensor& t, const char* name) {
   if (!t.defined() || t.numel() == 0) return nullptr;
-  TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kInt && t.is_contiguous(), name,
+  FO_CHECK(t.is_cuda() && t.scalar_type() == at::kInt && t.is_contiguous(), name,
               " must be a contiguous int32 CUDA tensor");
   return t.data_ptr<int>();
 }
@@ -69,17 +70,17 @@ inline void setup_problem(int algo, const at::Tensor& A, const at::Tensor& B, in
     p->N = s.N;
     p->K = s.K;
     const std::string err = prepare_tiling(algo, p);
-    TORCH_CHECK(err.empty(), err, " (M=", s.M, " N=", s.N, " K=", s.K, " Algo=", algo, ")");
+    FO_CHECK(err.empty(), err, " (M=", s.M, " N=", s.N, " K=", s.K, " Algo=", algo, ")");
     *bf16 = s.bf16;
   } else {
-    TORCH_CHECK(p->M == s.M && p->N == s.N && p->K == s.K && *bf16 == s.bf16,
+    FO_CHECK(p->M == s.M && p->N == s.N && p->K == s.K && *bf16 == s.bf16,
                 "all ranks of a loopback launch must use the same shape and dtype");
   }
   const AlgoConfig c = algo_config(algo);
   std::string e = encode_tmap_16bit(&maps->a[vr], A.data_ptr(), s.M, s.K, kBM);
-  TORCH_CHECK(e.empty(), "A: ", e);
-  e = encode_tmap_16bit(&maps->b[vr], B.data_ptr(), s.N, s.K, c.bn);
-  TORCH_CHECK(e.empty(), "B: ", e);
+  FO_CHECK(e.empty(), "A: ", e);
+  e = encode_tmap_16bit(&maps->b[vr], B.data_ptr(), s.N, s.K, c.cta2 ? c.bn / 2 : c.bn);
+  FO_CHECK(e.empty(), "B: ", e);
 }
 
 }  // namespace fo

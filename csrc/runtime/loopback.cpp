@@ -17,17 +17,18 @@ std::vector<int64_t> fused_loopback(std::string comm_op, std::vector<at::Tensor>
   const at::Tensor RA = RA_opt.has_value() ? *RA_opt : at::Tensor();
   const at::Tensor cseg_gpu = cseg_opt.has_value() ? *cseg_opt : at::Tensor();
   const int ws = static_cast<int>(A.size());
-  TORCH_CHECK(ws >= 2 && ws <= kMaxVirtualRanks, "loopback supports 2..", kMaxVirtualRanks, " ranks");
-  TORCH_CHECK(static_cast<int>(B.size()) == ws && static_cast<int>(out.size()) == ws,
+  FO_CHECK(ws >= 2 && ws <= kMaxVirtualRanks, "loopback supports 2..", kMaxVirtualRanks, " ranks");
+  FO_CHECK(static_cast<int>(B.size()) == ws && static_cast<int>(out.size()) == ws,
               "A, B and out must have one tensor per rank");
-  TORCH_CHECK(kBM % ws == 0, "rank count must divide 128");
+  FO_CHECK(kBM % ws == 0, "rank count must divide 128");
   int comm;
   if (comm_op == "all_reduce") {
     comm = kCommFusedAR;
   } else if (comm_op == "reduce_scatter") {
     comm = kCommFusedRS;
   } else {
-    TORCH_CHECK(false, "comm_op must be 'all_reduce' or 'reduce_scatter'");
+    FO_CHECK(false, "comm_op must be 'all_reduce' or 'reduce_scatter'");
+    comm = kCommFusedAR;
   }
   c10::cuda::CUDAGuard guard(A[0].device());
   cudaStream_t stream = c10::cuda::getCurrentCUDAStream().stream();
@@ -36,6 +37,8 @@ std::vector<int64_t> fused_loopback(std::string comm_op, std::vector<at::Tensor>
   cudaDeviceProp prop;
   cuda_check(cudaGetDeviceProperties(&prop, dev), "cudaGetDeviceProperties");
 
+  FO_CHECK(!algo_config(static_cast<int>(algo)).cta2,
+           "the loopback emulation runs single-CTA Algos only (Algo & 3 != 1)");
   GemmTensorMaps maps;
   GemmParams p;
   std::memset(&p, 0, sizeof(p));
@@ -45,7 +48,7 @@ std::vector<int64_t> fused_loopback(std::string comm_op, std::vector<at::Tensor>
   const int* cseg = int_ptr_or_null(cseg_gpu, "cseg_gpu");
   const int ngroups = cseg != nullptr ? static_cast<int>(cseg_gpu.numel()) : 0;
   const size_t nflags = ngroups > 0 ? ngroups : p.num_tiles;
-  TORCH_CHECK(nflags <= kSignalMaxFlags, "too many flags");
+  FO_CHECK(nflags <= kSignalMaxFlags, "too many flags");
   const size_t full_bytes = static_cast<size_t>(p.M) * p.N * 2;
   const int64_t out_elems = comm == kCommFusedAR ? static_cast<int64_t>(p.M) * p.N
                                                  : static_cast<int64_t>(p.M) * p.N / ws;

@@ -35,13 +35,14 @@ ncclDataType_t OverlapImpl::nccl_dtype(const at::Tensor& t) const {
   if (t.scalar_type() == at::kBFloat16) return ncclBfloat16;
   if (t.scalar_type() == at::kHalf) return ncclFloat16;
   if (t.scalar_type() == at::kFloat) return ncclFloat32;
-  TORCH_CHECK(false, "unsupported dtype for a collective");
+  FO_CHECK(false, "unsupported dtype for a collective");
+  return ncclFloat16;
 }
 
 void OverlapImpl::NcclInit(int64_t rank, int64_t world, std::vector<int64_t> id) {
-  TORCH_CHECK(world >= 1 && world <= kMaxRanks, "world size must be in [1, ", kMaxRanks, "]");
-  TORCH_CHECK(rank >= 0 && rank < world, "rank out of range");
-  TORCH_CHECK(comm_ == nullptr && heap_ == nullptr, "nccl_init was already called");
+  FO_CHECK(world >= 1 && world <= kMaxRanks, "world size must be in [1, ", kMaxRanks, "]");
+  FO_CHECK(rank >= 0 && rank < world, "rank out of range");
+  FO_CHECK(comm_ == nullptr && heap_ == nullptr, "nccl_init was already called");
   rank_ = static_cast<int>(rank);
   world_ = static_cast<int>(world);
   cuda_check(cudaGetDevice(&device_), "cudaGetDevice");
@@ -77,18 +78,18 @@ void OverlapImpl::OverlapInit() {
 
 void OverlapImpl::SetOption(std::string name, int64_t value) {
   if (name == "mode") {
-    TORCH_CHECK(value == 0 || value == 1, "mode must be 0 (fused) or 1 (gated)");
+    FO_CHECK(value == 0 || value == 1, "mode must be 0 (fused) or 1 (gated)");
     opt_mode_ = value;
   } else if (name == "strided_rows") {
     opt_strided_rows_ = value ? 1 : 0;
   } else if (name == "sm_margin") {
-    TORCH_CHECK(value >= 0 && value < sm_count_, "sm_margin out of range");
+    FO_CHECK(value >= 0 && value < sm_count_, "sm_margin out of range");
     opt_sm_margin_ = value;
   } else if (name == "timeout_ms") {
-    TORCH_CHECK(value > 0, "timeout_ms must be positive");
+    FO_CHECK(value > 0, "timeout_ms must be positive");
     opt_timeout_ms_ = value;
   } else {
-    TORCH_CHECK(false, "unknown option '", name, "'");
+    FO_CHECK(false, "unknown option '", name, "'");
   }
 }
 
@@ -101,11 +102,12 @@ int64_t OverlapImpl::GetOption(std::string name) {
   if (name == "rank") return rank_;
   if (name == "world") return world_;
   if (name == "num_algos") return kNumAlgos;
-  TORCH_CHECK(false, "unknown option '", name, "'");
+  FO_CHECK(false, "unknown option '", name, "'");
+  return 0;
 }
 
 at::Tensor OverlapImpl::SymmEmpty(std::vector<int64_t> sizes, std::string dtype) {
-  TORCH_CHECK(heap_ != nullptr, "call nccl_init first");
+  FO_CHECK(heap_ != nullptr, "call nccl_init first");
   at::ScalarType st;
   if (dtype == "bfloat16" || dtype == "bf16") {
     st = at::kBFloat16;
@@ -114,11 +116,12 @@ at::Tensor OverlapImpl::SymmEmpty(std::vector<int64_t> sizes, std::string dtype)
   } else if (dtype == "float32" || dtype == "fp32") {
     st = at::kFloat;
   } else {
-    TORCH_CHECK(false, "unsupported dtype '", dtype, "'");
+    FO_CHECK(false, "unsupported dtype '", dtype, "'");
+    st = at::kHalf;
   }
   int64_t numel = 1;
   for (int64_t s : sizes) {
-    TORCH_CHECK(s >= 0, "negative size");
+    FO_CHECK(s >= 0, "negative size");
     numel *= s;
   }
   const size_t bytes = std::max<size_t>(static_cast<size_t>(numel) * c10::elementSize(st), 256);
@@ -129,7 +132,7 @@ at::Tensor OverlapImpl::SymmEmpty(std::vector<int64_t> sizes, std::string dtype)
 }
 
 std::vector<int64_t> OverlapImpl::ReadStatus() {
-  TORCH_CHECK(status_.defined(), "call nccl_init first");
+  FO_CHECK(status_.defined(), "call nccl_init first");
   at::Tensor h = status_.cpu();
   std::vector<int64_t> out(kStatusWords);
   for (int i = 0; i < kStatusWords; ++i) out[i] = h.data_ptr<int>()[i];
@@ -138,13 +141,13 @@ std::vector<int64_t> OverlapImpl::ReadStatus() {
 
 void OverlapImpl::CheckStatus() {
   const std::vector<int64_t> s = ReadStatus();
-  TORCH_CHECK(s[kStatusWordCode] == kStatusOk, "flashoverlap device status: ",
+  FO_CHECK(s[kStatusWordCode] == kStatusOk, "flashoverlap device status: ",
               status_name(static_cast<int32_t>(s[kStatusWordCode])), " (args ", s[kStatusWordArg0],
               ", ", s[kStatusWordArg1], ", ", s[kStatusWordArg2], ") on rank ", rank_);
 }
 
 void OverlapImpl::ResetStatus() {
-  TORCH_CHECK(status_.defined(), "call nccl_init first");
+  FO_CHECK(status_.defined(), "call nccl_init first");
   status_.zero_();
   if (signal_ != nullptr) {
     char* base = static_cast<char*>(signal_->local());
@@ -184,7 +187,8 @@ void OverlapImpl::run_plain(const at::Tensor& A, const at::Tensor& B, void* out,
   p.out[0] = out;
   p.MM[0] = MM;
   p.status[0] = status_.data_ptr<int>();
-  const int grid = std::max(1, std::min(std::min(grid_cap, sm_count_), p.num_tiles));
+  const int resident = gemm_max_resident_ctas(algo, bf16, false);
+  const int grid = std::max(1, std::min(std::min(grid_cap, resident), p.num_tiles));
   cuda_check(launch_gemm(algo, bf16, false, maps, p, grid, 1, false, stream()), "GEMM launch");
 }
 
@@ -207,7 +211,7 @@ void OverlapImpl::SegAllReduce(at::Tensor C, at::Tensor cSEG_CPU, int64_t SegNum
   // Equal units of numel / SegNum elements; segment s covers cSEG_CPU[s] units
   // (reference: src/overlap_impl.cu:153-168).
   if (world_ == 1) return;
-  TORCH_CHECK(!cSEG_CPU.is_cuda() && cSEG_CPU.scalar_type() == at::kInt, "cSEG_CPU: int32 host tensor");
+  FO_CHECK(!cSEG_CPU.is_cuda() && cSEG_CPU.scalar_type() == at::kInt, "cSEG_CPU: int32 host tensor");
   const int* seg = cSEG_CPU.data_ptr<int>();
   const int64_t unit = C.numel() / SegNum;
   char* base = static_cast<char*>(C.data_ptr());
@@ -238,7 +242,7 @@ void OverlapImpl::NcclAll2All(at::Tensor C, at::Tensor D, at::Tensor mLen_CPU) {
   // receives mLen[i][r] rows from it; a rank's own rows are not part of C or D
   // (reference: src/overlap_impl.cu:181-212).
   if (world_ == 1) return;
-  TORCH_CHECK(!mLen_CPU.is_cuda() && mLen_CPU.scalar_type() == at::kInt &&
+  FO_CHECK(!mLen_CPU.is_cuda() && mLen_CPU.scalar_type() == at::kInt &&
                   mLen_CPU.numel() == static_cast<int64_t>(world_) * world_,
               "mLen_CPU must be an int32 host tensor of shape [world, world]");
   const int* ml = mLen_CPU.data_ptr<int>();
@@ -291,8 +295,8 @@ void OverlapImpl::GemmAll2All(at::Tensor A, at::Tensor B, at::Tensor C, at::Tens
 // ---------------------------------------------------------------------------- fused path
 
 void OverlapImpl::ensure_fused_buffers(size_t stage_bytes, size_t nflags) {
-  TORCH_CHECK(heap_ != nullptr, "call nccl_init first");
-  TORCH_CHECK(nflags <= kSignalMaxFlags, "too many tiles/groups for the flag region: ", nflags);
+  FO_CHECK(heap_ != nullptr, "call nccl_init first");
+  FO_CHECK(nflags <= kSignalMaxFlags, "too many tiles/groups for the flag region: ", nflags);
   if (signal_ == nullptr) signal_ = heap_->allocate(kSignalBytes, stream());
   if (stage_ == nullptr || stage_->bytes < stage_bytes) {
     // A larger shape than any seen so far: take a new region (the old one stays mapped until
@@ -304,15 +308,15 @@ void OverlapImpl::ensure_fused_buffers(size_t stage_bytes, size_t nflags) {
 void OverlapImpl::run_fused(int comm, const at::Tensor& A, const at::Tensor& B, at::Tensor out,
                             int out_mode, const int* RA, int rldn, int* MM, int mm_stride,
                             bool monitor, const int* cseg, int num_groups, int algo) {
-  TORCH_CHECK(heap_ != nullptr, "call nccl_init first");
+  FO_CHECK(heap_ != nullptr, "call nccl_init first");
   c10::cuda::CUDAGuard guard(A.device());
-  TORCH_CHECK(kBM % world_ == 0, "world size must divide the tile height 128");
+  FO_CHECK(kBM % world_ == 0, "world size must divide the tile height 128");
   GemmTensorMaps maps;
   GemmParams p;
   std::memset(&p, 0, sizeof(p));
   bool bf16 = true;
   setup_problem(algo, A, B, 0, &maps, &p, &bf16);
-  TORCH_CHECK(rldn == 1 || comm == kCommFusedAR, "reduce-scatter requires rLDN == 1");
+  FO_CHECK(rldn == 1 || comm == kCommFusedAR, "reduce-scatter requires rLDN == 1");
 
   const size_t full_bytes = static_cast<size_t>(p.M) * p.N * 2;
   const size_t nflags = (num_groups > 0 && cseg != nullptr) ? num_groups : p.num_tiles;
@@ -362,7 +366,7 @@ void OverlapImpl::run_fused(int comm, const at::Tensor& A, const at::Tensor& B, 
     p.flags[r] = reinterpret_cast<uint32_t*>(sig + kSignalFlagsOffset);
     p.done[r] = reinterpret_cast<uint32_t*>(sig + kSignalDoneOffset);
   }
-  const int grid = std::max(1, std::min(sm_count_, p.num_tiles));
+  const int grid = std::max(1, std::min(gemm_max_resident_ctas(algo, bf16, true), p.num_tiles));
   cuda_check(launch_gemm(algo, bf16, true, maps, p, grid, 1, false, stream()), "fused GEMM launch");
   if (copy_back) {
     cuda_check(cudaMemcpyAsync(out.data_ptr(), out_->local(), out_bytes, cudaMemcpyDeviceToDevice,
@@ -393,7 +397,7 @@ void OverlapImpl::GemmReduceScatterFused(at::Tensor A, at::Tensor B, at::Tensor 
 
 namespace {
 int* mm_ptr(const at::Tensor& MM) {
-  TORCH_CHECK(MM.is_cuda() && MM.scalar_type() == at::kInt && MM.is_contiguous(),
+  FO_CHECK(MM.is_cuda() && MM.scalar_type() == at::kInt && MM.is_contiguous(),
               "MM must be a contiguous int32 CUDA tensor");
   return MM.data_ptr<int>();
 }
@@ -437,7 +441,7 @@ void OverlapImpl::GemmReduceScatterOverlap(at::Tensor A, at::Tensor B, at::Tenso
   const int* ra = int_ptr_or_null(RA, "RA");
   const int* cseg = int_ptr_or_null(cSEG_GPU, "cSEG_GPU");
   const int ngroups = cseg != nullptr ? static_cast<int>(cSEG_GPU.numel()) : 0;
-  TORCH_CHECK(rLDN == 1, "reduce-scatter requires rLDN == 1");
+  FO_CHECK(rLDN == 1, "reduce-scatter requires rLDN == 1");
   if (opt_mode_ == 1 && world_ > 1) {
     gated_overlap(kCommFusedRS, A, B, C, D, MM, RA, RE, rLDN, cSEG_CPU, cSEG_GPU, Algo, if_monitor);
     return;
@@ -466,16 +470,16 @@ void OverlapImpl::gated_overlap(int comm, at::Tensor A, at::Tensor B, at::Tensor
   const AlgoConfig c = algo_config(static_cast<int>(Algo));
   const int tn = s.N / c.bn;
   const int tiles = (s.M / c.bm) * tn;
-  TORCH_CHECK(!cSEG_CPU.is_cuda() && cSEG_CPU.scalar_type() == at::kInt, "cSEG_CPU: int32 host tensor");
+  FO_CHECK(!cSEG_CPU.is_cuda() && cSEG_CPU.scalar_type() == at::kInt, "cSEG_CPU: int32 host tensor");
   const int* seg = cSEG_CPU.data_ptr<int>();
   const int ngroups = static_cast<int>(cSEG_CPU.numel());
   const int* cseg_gpu = int_ptr_or_null(cSEG_GPU, "cSEG_GPU");
-  TORCH_CHECK(cseg_gpu != nullptr && cSEG_GPU.numel() == ngroups, "cSEG_GPU must mirror cSEG_CPU");
+  FO_CHECK(cseg_gpu != nullptr && cSEG_GPU.numel() == ngroups, "cSEG_GPU must mirror cSEG_CPU");
   int* mm = mm_ptr(MM);
-  TORCH_CHECK(MM.numel() >= ngroups, "MM has fewer counters than there are groups");
+  FO_CHECK(MM.numel() >= ngroups, "MM has fewer counters than there are groups");
   const bool rs = comm == kCommFusedRS;
   const int* re = rs ? int_ptr_or_null(RE, "RE") : nullptr;
-  TORCH_CHECK(!rs || re != nullptr, "RE is required for reduce-scatter");
+  FO_CHECK(!rs || re != nullptr, "RE is required for reduce-scatter");
 
   cudaStream_t gs = stream();
   // Counters are consumed by this call only once the GEMM stream has reached this point

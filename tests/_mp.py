@@ -36,7 +36,7 @@ def _entry(rank, world, backend, port, fn, args, result_dir, timeout_s):
         raise
 
 
-def run_ranks(fn, world: int, backend: str = "gloo", args=(), timeout_s: int = 120):
+def run_ranks(fn, world: int, backend: str = "gloo", args=(), timeout_s: int = 60):
     """Runs fn(rank, world, *args) in `world` processes; returns the per-rank results."""
     with tempfile.TemporaryDirectory() as d:
         try:

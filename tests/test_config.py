@@ -8,10 +8,10 @@ from flashoverlap_b200.utils import config, layout
 
 def test_algo_table_matches_native(lib):
     flat = list(torch.ops.flashoverlap_op.algo_table())
-    assert len(flat) == 5 * config.NUM_ALGOS
+    assert len(flat) == 6 * config.NUM_ALGOS
     for a in range(config.NUM_ALGOS):
         p = config.algo_params(a)
-        assert tuple(flat[5 * a:5 * a + 5]) == (p["BM"], p["BN"], p["BK"], p["stages"], p["raster"])
+        assert tuple(flat[6 * a:6 * a + 6]) == (p["BM"], p["BN"], p["BK"], p["stages"], p["raster"], p["cta2"])
 
 
 def test_algo_dict_roundtrip(tmp_path):

@@ -39,7 +39,7 @@ def _fused_worker(rank, world):
     dev = torch.device("cuda", rank)
     impl = _setup(rank, world)
     res = {}
-    for (M, N, K, algo) in ((1024, 2048, 512, 0), (2048, 1024, 256, 6)):
+    for (M, N, K, algo) in ((1024, 2048, 512, 0), (2048, 1024, 256, 6), (2048, 2048, 512, 1)):
         p = config.algo_params(algo)
         BM, BN = p["BM"], p["BN"]
         tiles = (M // BM) * (N // BN)
@@ -47,7 +47,7 @@ def _fused_worker(rank, world):
         ref = A.float() @ B.float().t()
         dist.all_reduce(ref)
         tol = 0.02 * ref.abs().max().item() + 1e-3
-        hint = layout.analytic_hint(M, N, BM, BN, p["raster"])
+        hint = layout.analytic_hint(M, N, BM, BN, p["raster"], bool(p["cta2"]))
         RA = layout.reorder_indices(tiles, hint, device=dev).reshape(M // BM, N // BN)
         mm = torch.zeros(1, N // BN, device=dev, dtype=torch.int32)
         e, eg = torch.empty(0, dtype=torch.int32), torch.empty(0, dtype=torch.int32, device=dev)
@@ -135,7 +135,7 @@ def _api_worker(rank, world):
     # counter-gated NCCL mechanism (the reference's scheme) on both collectives
     impl.set_option("mode", 1)
     wave = impl.get_option("sm_count") - impl.get_option("sm_margin")
-    hint = layout.analytic_hint(M, N, BM, BN, p["raster"])
+    hint = layout.analytic_hint(M, N, BM, BN, p["raster"], bool(p["cta2"]))
     cseg = layout.cseg_from_wave_groups(tiles, max(1, min(wave, tiles // 2)), [1] * layout.div_up(tiles, max(1, min(wave, tiles // 2))))
     RA = layout.reorder_indices(tiles, hint, device=dev).reshape(M // BM, N // BN)
     mm = torch.zeros(1, max(N // BN, len(cseg)), device=dev, dtype=torch.int32)
@@ -213,12 +213,14 @@ def _timeout_worker(rank, world):
     import time
     dev = torch.device("cuda", rank)
     impl = _setup(rank, world)
-    impl.set_option("timeout_ms", 300)
     M, N, K = 256, 512, 128
     A, B = _rand((M, K), dev, 1), _rand((N, K), dev, 2)
     C = impl.symm_empty([M, N], "bfloat16")
     out = {"elapsed": 0.0, "status": [0] * 8}
+    # one complete call first: the symmetric staging memory is allocated collectively
+    impl.gemm_allreduce_fused(A, B, C, 0)
     torch.cuda.synchronize(); dist.barrier()
+    impl.set_option("timeout_ms", 300)
     if rank == 0:
         t = time.time()
         impl.gemm_allreduce_fused(A, B, C, 0)
