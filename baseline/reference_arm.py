@@ -22,7 +22,8 @@ REF_LIB = os.path.join(REF_DIR, "lib", "libst_pybinding.so")
 
 def unavailable(why: str) -> None:
     if int(os.environ.get("RANK", "0")) == 0:
-        print(json.dumps({"impl": "reference", "unavailable": why}), flush=True)
+        import bench
+        print(json.dumps({"impl": "reference", "unavailable": why}), file=bench.REAL_STDOUT, flush=True)
 
 
 def main(args) -> None:

@@ -30,7 +30,9 @@ sys.path.insert(0, ROOT)
 
 M_AR, N_AR, K_AR_TOTAL = 8192, 8192, 28672
 M_RS, N_RS, K_RS_TOTAL = 16384, 8192, 8192
+WARM_SECONDS = 0.4
 NVLINK_GBS = 770.0           # measured peer-copy bandwidth per direction per GPU on this pool
+REAL_STDOUT = sys.stdout
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
@@ -138,7 +140,20 @@ def time_steps(torch, dist, world, fn, steps, warmup, flush, sampler=None):
     """Per-step CUDA events on the launching stream, L2 flushed between steps (outside the
     event pairs), barrier + synchronize on both sides.  Returns (mean ms over steps, max over
     ranks), the clock record and the wall time of the bracket."""
+    # Warm up by count AND by time: the GPU settles at its power-capped clocks only after a few
+    # hundred milliseconds of load, and every arm must be measured in that state.  The number of
+    # extra warm-up steps is agreed on by all ranks so that everybody runs the same sequence.
+    torch.cuda.synchronize()
+    t_warm = time.perf_counter()
     for _ in range(warmup):
+        fn()
+        flush()
+    torch.cuda.synchronize()
+    per_step = torch.tensor([(time.perf_counter() - t_warm) / max(1, warmup)], device="cuda")
+    if world > 1:
+        dist.all_reduce(per_step, op=dist.ReduceOp.MAX)
+    extra_warm = int(min(2000, max(0.0, WARM_SECONDS / max(per_step.item(), 1e-5) - warmup)))
+    for _ in range(extra_warm):
         fn()
         flush()
     ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
@@ -298,7 +313,7 @@ def run_ours(args):
 
     if not args.no_extra:
         try:
-            extra.update(extras(torch, dist, impl, rank, world, dev, A, B, C, algo, flush, peaks))
+            extra.update(extras(torch, dist, impl, rank, world, dev, A, B, C, algo, flush, peaks, args.steps))
         except Exception as ex:  # extras never block the headline line
             extra["extras_error"] = repr(ex)[:300]
 
@@ -320,13 +335,13 @@ def run_ours(args):
         "extra": extra,
     }
     if rank == 0:
-        print(json.dumps(line), flush=True)
+        print(json.dumps(line), file=REAL_STDOUT, flush=True)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
 
 
-def extras(torch, dist, impl, rank, world, dev, A, B, C, algo, flush, peaks):
+def extras(torch, dist, impl, rank, world, dev, A, B, C, algo, flush, peaks, steps_main):
     """Comparison arms on the same box: our GEMM then one NCCL call (non-overlap), cuBLAS + NCCL,
     the counter-gated NCCL mechanism, and the GEMM+ReduceScatter+RMSNorm config."""
     from flashoverlap_b200 import ops
@@ -334,7 +349,7 @@ def extras(torch, dist, impl, rank, world, dev, A, B, C, algo, flush, peaks):
     from flashoverlap_b200.utils import config, layout
 
     out = {}
-    steps, warm = 20, 5
+    steps, warm = max(20, min(steps_main, 100)), 5
     M, N = A.shape[0], B.shape[0]
     Cn = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
     ms, _, _ = time_steps(torch, dist, world, lambda: impl.gemm_allreduce(A, B, Cn, algo), steps, warm, flush)
@@ -346,6 +361,12 @@ def extras(torch, dist, impl, rank, world, dev, A, B, C, algo, flush, peaks):
     out["cublas_gemm_only_ms"] = round(ms, 5)
     ms, _, _ = time_steps(torch, dist, world, lambda: impl.cutlass_gemm(A, B, Cn, algo), steps, warm, flush)
     out["our_gemm_only_ms"] = round(ms, 5)
+    if world > 1:
+        Dn = torch.empty(M // world, N, device=dev, dtype=torch.bfloat16)
+        ms, _, _ = time_steps(torch, dist, world, lambda: impl.gemm_reducescatter_fused(A, B, Dn, algo), steps, warm, flush)
+        out["fused_rs_same_shape_ms"] = round(ms, 5)
+        ms, _, _ = time_steps(torch, dist, world, lambda: impl.gemm_allreduce_fused(A, B, C, algo), steps, warm, flush)
+        out["fused_ar_natural_ms"] = round(ms, 5)
     if world > 1:
         cfg = config.default_solution(M, N, algo, wave_size=148 - 16)
         tiles = (M // cfg["BM"]) * (N // cfg["BN"])
@@ -410,7 +431,18 @@ def run_reference(args):
     reference_arm.main(args)
 
 
+def _claim_stdout():
+    """Only the JSON line may reach stdout: libraries (NCCL prints its version there) are sent
+    to stderr by pointing fd 1 at fd 2; the returned file object writes to the real stdout."""
+    sys.stdout.flush()
+    real = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
+    return real
+
+
 def main():
+    global REAL_STDOUT
+    REAL_STDOUT = _claim_stdout()
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
