@@ -1,1 +1,1 @@
-from . import config, layout  # noqa: F401
+from . import config, layout, timing  # noqa: F401

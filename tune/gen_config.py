@@ -1,0 +1,75 @@
+#!/usr/bin/env python
+"""Stage 1 of tuning from a list of candidate kernels in a CSV file.
+
+    python tune/gen_config.py --m 4096 --n 8192 --k 8192 [--csv m4096n8192k8192.gemm.csv]
+
+The reference feeds this step with the CUTLASS profiler's CSV (tune/gen_config.py:46-120): it
+takes the 10 fastest rows, maps their tile parameters to an Algo index through ``AlgoDict.pt``
+and re-times them under its wrapper.  There is no external profiler for a hand-written kernel
+family, so the CSV here is any table with the columns ``cta_m, cta_n, cta_k, stages, raster,
+cta_group`` (one candidate per row, optional ``runtime`` column used only for the initial sort);
+rows that do not name an existing Algo are reported and skipped.  Without ``--csv`` every Algo is
+a candidate.  Output is identical to ``profile_config.py``.
+"""
+import argparse
+import csv
+import heapq
+
+from _common import REP, WARM_UP, config, dtype_of, make_operands, torch
+
+from flashoverlap_b200 import ops
+from flashoverlap_b200.utils.timing import perf_ms
+
+
+def candidates_from_csv(path):
+    table = config.algo_dict()
+    rows = []
+    with open(path) as f:
+        for row in csv.DictReader(f):
+            rows.append(row)
+    rows.sort(key=lambda r: float(r.get("runtime", 0) or 0))
+    out = []
+    for r in rows[:10]:
+        bm, bn, bk = int(r["cta_m"]), int(r["cta_n"]), int(r["cta_k"])
+        grp = int(r.get("cta_group", 1) or 1)
+        key = (bm, bn, bk, 128 * grp, bn, 16, grp, 2, 64, int(r["stages"]), int(r["raster"]), 1)
+        if key in table:
+            out.append(table[key])
+        else:
+            print(f"no kernel for {key}: this library ships a fixed Algo table, skipping")
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--m", type=int, default=4096)
+    ap.add_argument("--n", type=int, default=8192)
+    ap.add_argument("--k", type=int, default=8192)
+    ap.add_argument("--csv", default=None)
+    ap.add_argument("--dtype", default="bf16")
+    ap.add_argument("--path", default=None)
+    args = ap.parse_args()
+    torch.cuda.set_device(0)
+    dt = dtype_of(args.dtype)
+    algos = candidates_from_csv(args.csv) if args.csv else list(range(config.NUM_ALGOS))
+    impl = ops.OverlapImpl()
+    impl.nccl_init(0, 1, [0] * 16)
+    impl.cutlass_init()
+    A, B = make_operands(args.m, args.n, args.k, dt, "cuda")
+    C = torch.empty(args.m, args.n, device="cuda", dtype=dt)
+    timed = []
+    for algo in algos:
+        p = config.algo_params(algo)
+        if args.n % p["BN"] or args.m % (p["BM"] * (2 if p["cta2"] else 1)):
+            continue
+        timed.append((perf_ms(lambda: impl.cutlass_gemm(A, B, C, algo), WARM_UP, REP, reduce_max=False), algo))
+    best = heapq.nsmallest(10, timed)
+    path = config.config_path(args.m, args.n, args.k, directory=args.path)
+    config.save_stage1(path, [config.algo_params(a)["BM"] for _, a in best],
+                       [config.algo_params(a)["BN"] for _, a in best], [t for t, _ in best], [a for _, a in best])
+    config.save_algo_dict(path.parent / "AlgoDict.pt")
+    print(f"wrote {path}")
+
+
+if __name__ == "__main__":
+    main()

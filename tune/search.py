@@ -1,0 +1,128 @@
+#!/usr/bin/env python
+"""Stage 2 of tuning: find the completion-order hint and the wave grouping (cSeg).
+
+    python tune/search.py --m 4096 --n 8192 --k 8192 --comm_op all_reduce
+    python tune/search.py --m 16384 --n 8192 --k 1024 --comm_op reduce_scatter --predictive_search true
+    python tune/search.py ... --mode gated          # tune the counter-gated NCCL mechanism instead
+
+Reads the stage-1 JSON written by ``profile_config.py`` / ``gen_config.py`` and rewrites it with
+scalars ``BM, BN, dur, Algo`` plus ``hint``, ``cSeg`` and ``rLDN`` (reference: tune/search.py:34-51,
+:387-502).  Differences that come with the B200 design:
+
+* the hint is known by construction (persistent kernel, static tile order); ``--verify_hint`` runs
+  the monitor mode and reports how many tiles land in the predicted wave;
+* ``--mode fused`` (default) tunes the in-kernel collective: candidates are the wave groupings plus
+  "one flag per tile"; ``--mode gated`` tunes the reference's mechanism (wave = SMs - sm_margin);
+* predictive search uses the matching bandwidth curve (``bandwidth_fused_*`` or ``bandwidth_*``)
+  and always ends with one real run of the winner; ``--compare`` additionally runs the exhaustive
+  search and prints predicted vs measured best.
+"""
+import argparse
+
+from _common import OverlapWorkload, config, dtype_of, layout, str2bool, torch
+
+from flashoverlap_b200 import tuner
+from flashoverlap_b200.parallel import bootstrap
+from flashoverlap_b200.parallel.launch import run_on_all_gpus
+from flashoverlap_b200.utils.timing import perf_ms
+
+
+def verify_hint(wl, grid):
+    """Fraction of tiles whose measured completion wave equals the analytic one."""
+    ident = torch.arange(wl.tiles, device=wl.dev, dtype=torch.int32).reshape(wl.RA.shape)
+    saved, wl.RA = wl.RA, ident
+    wl.MM.zero_()
+    wl.run(monitor=True)
+    torch.cuda.synchronize()
+    order = wl.MM[1:, : wl.N // wl.BN].flatten().cpu().long()
+    wl.RA = saved
+    wl.MM.zero_()
+    analytic = torch.empty(wl.tiles, dtype=torch.long)
+    analytic[torch.tensor(wl.hint)] = torch.arange(wl.tiles) // grid
+    return float(((order // grid) == analytic).float().mean())
+
+
+def worker(rank, world, args):
+    dt = dtype_of(args.dtype)
+    impl = bootstrap.make_overlap_impl(rank, world)
+    impl.set_option("timeout_ms", 20000)
+    path = config.config_path(args.m, args.n, args.k, directory=args.path)
+    cfg = config.load_config(path)
+    algos = cfg["Algo"] if isinstance(cfg["Algo"], list) else [cfg["Algo"]]
+    durs = cfg["dur"] if isinstance(cfg["dur"], list) else [cfg["dur"]]
+    sm = impl.get_option("sm_count")
+    margin = impl.get_option("sm_margin")
+    log = print if rank == 0 else (lambda *a, **k: None)
+
+    best = None
+    for algo, gemm_ms in list(zip(algos, durs))[: (5 if not args.predictive_search else 10)]:
+        wl = OverlapWorkload(impl, rank, world, args.m, args.n, args.k, algo, args.comm_op, dt, mode=args.mode)
+        wave = (sm - margin) if args.mode == "gated" else sm
+        if args.verify_hint:
+            log(f"Algo {algo}: hint agreement with monitor = {verify_hint(wl, min(wave, wl.tiles)):.3f}")
+        prob = tuner.Problem(args.m, args.n, wl.BM, wl.BN, gemm_ms, sm, world, args.comm_op, sm_margin=margin)
+        cands = tuner.candidate_groupings(wl.tiles, wave, max_waves_per_unit=(10 if args.predictive_search else 7))
+        if args.mode == "fused":
+            cands.append([1] * wl.tiles)
+
+        def measure(cseg):
+            wl.set_cseg(cseg)
+            return perf_ms(wl.run, args.warmup, args.reps)
+
+        predicted = None
+        if args.predictive_search or args.compare:
+            name = f"bandwidth_fused_{args.comm_op}_tp{world}.pt" if args.mode == "fused" else \
+                f"bandwidth_{args.comm_op}_tp{world}.pt"
+            curve = torch.load(path.parent / name)
+            cseg_p, t_p = tuner.predictive_search(prob, curve, args.mode, cands, wave)
+            t_real = measure(cseg_p)
+            predicted = (cseg_p, t_p, t_real)
+            log(f"Algo {algo}: predicted best {_short(cseg_p)} -> model {t_p:.4f} ms, measured {t_real:.4f} ms")
+        if not args.predictive_search or args.compare:
+            cseg_e, t_e, _ = tuner.exhaustive_search(cands, measure, log=lambda s: log("  " + s[-70:]))
+            log(f"Algo {algo}: exhaustive best {_short(cseg_e)} -> {t_e:.4f} ms")
+            result = (t_e, algo, gemm_ms, wl.hint, cseg_e, wl.BM, wl.BN, predicted)
+        else:
+            result = (predicted[2], algo, gemm_ms, wl.hint, predicted[0], wl.BM, wl.BN, predicted)
+        if best is None or result[0] < best[0]:
+            best = result
+        del wl
+        if not args.all_algos:
+            break
+    impl.check_status()
+    if rank == 0:
+        t, algo, gemm_ms, hint, cseg, BM, BN, predicted = best
+        config.save_solution(path, BM, BN, gemm_ms, algo, hint, cseg, 1, tp=world, comm_op=args.comm_op,
+                             dtype=args.dtype, mode=args.mode, overlap_ms=t)
+        print(f"Best solution: Algo {algo}, cSeg {_short(cseg)}, {t:.4f} ms. Solution saved to {path}")
+    return best
+
+
+def _short(cseg):
+    return cseg if len(cseg) <= 12 else f"[{cseg[0]}, {cseg[1]}, ... x{len(cseg)}]"
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--m", type=int, default=4096)
+    ap.add_argument("--k", type=int, default=8192)
+    ap.add_argument("--n", type=int, default=8192)
+    ap.add_argument("--comm_op", default="all_reduce", choices=["all_reduce", "reduce_scatter"])
+    ap.add_argument("--predictive_search", type=str2bool, default=False)
+    ap.add_argument("--mode", default="fused", choices=["fused", "gated"])
+    ap.add_argument("--compare", action="store_true", help="run both searches and report predicted vs exhaustive")
+    ap.add_argument("--verify_hint", action="store_true")
+    ap.add_argument("--all_algos", action="store_true", help="search the groupings of every stage-1 candidate")
+    ap.add_argument("--dtype", default="bf16")
+    ap.add_argument("--path", default=None)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--reps", type=int, default=50)
+    args = ap.parse_args()
+    # the reference forces the predictive search for large outputs (tune/search.py:519)
+    if args.m * args.n > 33554432 and not args.compare:
+        args.predictive_search = True
+    run_on_all_gpus(worker, args)
+
+
+if __name__ == "__main__":
+    main()
