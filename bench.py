@@ -443,6 +443,7 @@ def _claim_stdout():
 def main():
     global REAL_STDOUT
     REAL_STDOUT = _claim_stdout()
+    sys.modules.setdefault("bench", sys.modules[__name__])   # `import bench` elsewhere must see this module
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)

@@ -12,7 +12,7 @@ namespace fo {
 constexpr int kBM = 128;  // tile rows = UMMA M (one TMEM lane per row)
 constexpr int kBK = 64;   // 64 x 16-bit = one 128-byte swizzle atom along K
 constexpr int kMaxRanks = 8;
-constexpr int kMaxVirtualRanks = 4;
+constexpr int kMaxVirtualRanks = 8;
 
 enum OutMode : int {
   kOutNatural = 0,      // row-major [M, N]

@@ -77,7 +77,8 @@ __device__ __forceinline__ TileCoord tile_of_position(int pos, int tiles_m, int 
 
 // Wave group of reordered position r: groups are runs of cseg[g] consecutive positions.
 __device__ __forceinline__ void group_of_position(const GemmParams& p, int r, int* g, int* need) {
-  if (p.num_groups <= 0 || p.cseg == nullptr) {
+  // No grouping, or as many groups as tiles (every group then holds exactly one tile).
+  if (p.num_groups <= 0 || p.cseg == nullptr || p.num_groups == p.num_tiles) {
     *g = r;
     *need = 1;
     return;
@@ -574,7 +575,7 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
       }
       ptx::named_bar_sync(2, kReducerThreads);
       if (*s_is_last) {
-        const int nflags = (p.num_groups > 0 && p.cseg != nullptr) ? p.num_groups : p.num_tiles;
+        const int nflags = (p.num_groups > 0 && p.cseg != nullptr) ? p.num_groups : p.num_tiles;  // same count either way when equal
         for (int i = rt; i < nflags; i += kReducerThreads) p.flags[me][i] = 0u;
         ptx::named_bar_sync(2, kReducerThreads);
         if (rt == 0) {

@@ -69,7 +69,11 @@ __device__ __forceinline__ size_t reordered_offset(int b, int col, int dim, int 
          (col % BN);
 }
 
-// One CTA walks rows; each thread owns VPT 16-byte vectors of the row (VPT * 256 * 8 >= dim).
+// Each CTA takes a contiguous block of rows; each thread owns VPT 16-byte vectors of a row
+// (VPT * 256 * 8 >= dim).  Two things keep HBM busy: the next row's vectors are requested
+// before the current row is reduced (register double buffer), and in the reordered case the
+// tile look-up through RA - a dependent load in front of every data load - is done only when
+// the block of rows crosses into another row panel, not per row.
 template <bool BF16, bool REORDER, int VPT>
 __global__ void __launch_bounds__(kNormThreads)
     rmsnorm_kernel(const uint16_t* __restrict__ X, uint16_t* __restrict__ Y,
@@ -77,33 +81,60 @@ __global__ void __launch_bounds__(kNormThreads)
                    const int* __restrict__ RA, float eps) {
   __shared__ float red[kNormThreads / 32];
   const int nvec = dim / 8;
+  const int per_cta = (rows + gridDim.x - 1) / gridDim.x;
+  const int row_begin = blockIdx.x * per_cta;
+  const int row_end = min(rows, row_begin + per_cta);
+  if (row_begin >= row_end) return;
+
   uint4 wv[VPT];
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
     const int j = threadIdx.x + i * kNormThreads;
     if (j < nvec) wv[i] = *reinterpret_cast<const uint4*>(W + static_cast<size_t>(j) * 8);
   }
-  for (int b = blockIdx.x; b < rows; b += gridDim.x) {
-    uint4 xv[VPT];
+
+  // Element offset of (row 0 of the current panel, this thread's column) per vector.
+  size_t panel_off[VPT];
+  int panel = -1;
+  const size_t ld = REORDER ? static_cast<size_t>(rldn) * BN : static_cast<size_t>(dim);
+  auto load_row = [&](int b, uint4 (&dst)[VPT]) {
+    if constexpr (REORDER) {
+      const int pb = b / BM;
+      if (pb != panel) {
+        panel = pb;
 #pragma unroll
-    for (int i = 0; i < VPT; ++i) {
-      const int j = threadIdx.x + i * kNormThreads;
-      if (j < nvec) {
-        size_t off;
-        if constexpr (REORDER) {
-          off = reordered_offset(b, j * 8, dim, BM, BN, rldn, RA);
-        } else {
-          off = static_cast<size_t>(b) * dim + static_cast<size_t>(j) * 8;
+        for (int i = 0; i < VPT; ++i) {
+          const int j = threadIdx.x + i * kNormThreads;
+          if (j < nvec) panel_off[i] = reordered_offset(pb * BM, j * 8, dim, BM, BN, rldn, RA);
         }
-        xv[i] = __ldcs(reinterpret_cast<const uint4*>(X + off));  // streamed: read once
+      }
+      const size_t row_off = static_cast<size_t>(b - pb * BM) * ld;
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        const int j = threadIdx.x + i * kNormThreads;
+        if (j < nvec) dst[i] = __ldcs(reinterpret_cast<const uint4*>(X + panel_off[i] + row_off));
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        const int j = threadIdx.x + i * kNormThreads;
+        if (j < nvec)
+          dst[i] = __ldcs(reinterpret_cast<const uint4*>(X + static_cast<size_t>(b) * dim +
+                                                         static_cast<size_t>(j) * 8));
       }
     }
+  };
+
+  uint4 cur[VPT], nxt[VPT];
+  load_row(row_begin, cur);
+  for (int b = row_begin; b < row_end; ++b) {
+    if (b + 1 < row_end) load_row(b + 1, nxt);
     float ss = 0.f;
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
       const int j = threadIdx.x + i * kNormThreads;
       if (j < nvec) {
-        const uint32_t* u = reinterpret_cast<const uint32_t*>(&xv[i]);
+        const uint32_t* u = reinterpret_cast<const uint32_t*>(&cur[i]);
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
           const float2 f = unpack2<BF16>(u[k]);
@@ -118,13 +149,15 @@ __global__ void __launch_bounds__(kNormThreads)
       const int j = threadIdx.x + i * kNormThreads;
       if (j < nvec) {
         uint4 y;
-        y.x = scale_mul2<BF16>(xv[i].x, wv[i].x, scale);
-        y.y = scale_mul2<BF16>(xv[i].y, wv[i].y, scale);
-        y.z = scale_mul2<BF16>(xv[i].z, wv[i].z, scale);
-        y.w = scale_mul2<BF16>(xv[i].w, wv[i].w, scale);
-        *reinterpret_cast<uint4*>(Y + static_cast<size_t>(b) * dim + static_cast<size_t>(j) * 8) = y;
+        y.x = scale_mul2<BF16>(cur[i].x, wv[i].x, scale);
+        y.y = scale_mul2<BF16>(cur[i].y, wv[i].y, scale);
+        y.z = scale_mul2<BF16>(cur[i].z, wv[i].z, scale);
+        y.w = scale_mul2<BF16>(cur[i].w, wv[i].w, scale);
+        __stcs(reinterpret_cast<uint4*>(Y + static_cast<size_t>(b) * dim + static_cast<size_t>(j) * 8), y);
       }
     }
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) cur[i] = nxt[i];
   }
 }
 
@@ -154,7 +187,10 @@ cudaError_t launch_norm(const void* X, void* Y, const void* W, int rows, int dim
                         int rldn, const int* RA, float eps, int sm_count, cudaStream_t stream) {
   const int nvec = dim / 8;
   const int vpt = (nvec + kNormThreads - 1) / kNormThreads;
+  // contiguous row blocks: enough CTAs to fill the machine several times over, yet a few
+  // rows per CTA so that the prefetch and the cached tile look-ups pay off
   int grid = rows < sm_count * 8 ? rows : sm_count * 8;
+  if (rows >= sm_count * 32) grid = (rows + 3) / 4 < sm_count * 16 ? (rows + 3) / 4 : sm_count * 16;
   if (grid < 1) grid = 1;
   const uint16_t* x = static_cast<const uint16_t*>(X);
   uint16_t* y = static_cast<uint16_t*>(Y);

@@ -26,11 +26,12 @@ def worker(rank, world, args):
     path = config.config_path(M, N, K, directory=args.path)
     cfg = config.load_config(path) if path.exists() and config.is_tuned(config.load_config(path)) else \
         config.default_solution(M, N, args.algo)
-    g = torch.Generator(device="cuda").manual_seed(100 + rank)
-    A = (torch.randn(M, K, device="cuda", generator=g) * 0.5).to(dt)
-    B = (torch.randn(N, K, device="cuda", generator=g) * 0.5).to(dt)
-    gw = torch.Generator(device="cuda").manual_seed(7)
-    W = (1 + 0.02 * torch.randn(N, device="cuda", generator=gw)).to(dt)
+    dev = torch.device("cuda", torch.cuda.current_device())
+    g = torch.Generator(device=dev).manual_seed(100 + rank)
+    A = (torch.randn(M, K, device=dev, generator=g) * 0.5).to(dt)
+    B = (torch.randn(N, K, device=dev, generator=g) * 0.5).to(dt)
+    gw = torch.Generator(device=dev).manual_seed(7)
+    W = (1 + 0.02 * torch.randn(N, device=dev, generator=gw)).to(dt)
 
     norm = RMSNorm(N, eps=1e-5, dtype=dt)
     norm.weight = nn.Parameter(W)

@@ -25,23 +25,51 @@ def _free_port() -> int:
         return s.getsockname()[1]
 
 
-def _child(rank: int, world: int, port: int, fn: Callable, args: tuple, out_path: str) -> None:
+def _arm_watchdog() -> None:
+    """FLASHOVERLAP_HANG_DUMP=<seconds>: every rank dumps its Python stacks to stderr if it is
+    still running after that long, and again at the same interval - enough to see which
+    collective or synchronisation a stuck rank is sitting in."""
+    secs = float(os.environ.get("FLASHOVERLAP_HANG_DUMP", "0") or 0)
+    if secs > 0:
+        import faulthandler
+        import sys
+        faulthandler.dump_traceback_later(secs, repeat=True, file=sys.stderr)
+
+
+def _child(rank: int, world: int, port: int, fn: Callable, args: tuple, out_path: str, backend: str) -> None:
+    _arm_watchdog()
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), LOCAL_RANK=str(rank),
                       WORLD_SIZE=str(world))
-    torch.cuda.set_device(rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    if backend == "nccl":
+        torch.cuda.set_device(rank)
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    else:
+        dist.init_process_group(backend, rank=rank, world_size=world)
     try:
         res = fn(rank, world, *args)
-        if rank == 0:
-            torch.save(res, out_path)
-        dist.barrier()
-    finally:
-        dist.destroy_process_group()
+    except BaseException:
+        # The peers may be blocked in a collective that this rank will never join, and a clean
+        # process-group shutdown would wait for them: report and leave at once, the parent then
+        # terminates the other ranks.
+        import traceback
+        traceback.print_exc()
+        os._exit(1)
+    if rank == 0:
+        torch.save(res, out_path)
+    dist.barrier()
+    dist.destroy_process_group()
 
 
-def run_on_all_gpus(fn: Callable[..., Any], *args, nprocs: Optional[int] = None) -> Any:
+def run_on_all_gpus(fn: Callable[..., Any], *args, nprocs: Optional[int] = None, backend: str = "nccl") -> Any:
+    """``backend="gloo"`` with an explicit ``nprocs`` runs the same launcher on CPU ranks (tests)."""
+    if backend != "nccl":
+        with tempfile.TemporaryDirectory() as d:
+            out = os.path.join(d, "rank0.pt")
+            mp.spawn(_child, args=(nprocs, _free_port(), fn, args, out, backend), nprocs=nprocs, join=True)
+            return torch.load(out, weights_only=False) if os.path.exists(out) else None
     if "RANK" in os.environ and "WORLD_SIZE" in os.environ:
         from .bootstrap import init_distributed
+        _arm_watchdog()
         rank, world, _ = init_distributed()
         res = fn(rank, world, *args)
         if world > 1:
@@ -53,5 +81,5 @@ def run_on_all_gpus(fn: Callable[..., Any], *args, nprocs: Optional[int] = None)
         return fn(0, 1, *args)
     with tempfile.TemporaryDirectory() as d:
         out = os.path.join(d, "rank0.pt")
-        mp.spawn(_child, args=(world, _free_port(), fn, args, out), nprocs=world, join=True)
+        mp.spawn(_child, args=(world, _free_port(), fn, args, out, backend), nprocs=world, join=True)
         return torch.load(out, weights_only=False) if os.path.exists(out) else None

@@ -188,6 +188,13 @@ def test_fused_loopback(cuda, comm_op, ws, algo, strided, natural):
     _loopback_case(cuda, comm_op, ws, 1024, 2048, 512, algo, strided, natural)
 
 
+def test_fused_loopback_eight_ranks(cuda):
+    """Eight ranks (16 owned rows per tile each), 18 CTAs per rank, on one GPU."""
+    _loopback_case(cuda, "all_reduce", 8, 2048, 2048, 256, 0, True, False, repeat=2)
+    _loopback_case(cuda, "reduce_scatter", 8, 2048, 2048, 256, 2, True, True)
+    _loopback_case(cuda, "reduce_scatter", 8, 1024, 1024, 128, 0, False, False)
+
+
 def test_fused_loopback_repeat_groups_fp16(cuda):
     _loopback_case(cuda, "all_reduce", 2, 2048, 2048, 256, 0, True, False, repeat=3, groups=[40, 50, 38])
     _loopback_case(cuda, "reduce_scatter", 4, 2048, 2048, 256, 4, True, False, repeat=3)
