@@ -32,6 +32,7 @@ SOURCES = [
     "gemm/fo_gemm_launch.cu",
     "norm/fo_norm.cu",
     "flags/fo_wait.cu",
+    "noalloc/fo_noalloc.cu",
 ]
 
 CUDA_FLAGS = [
