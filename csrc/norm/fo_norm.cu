@@ -75,7 +75,7 @@ __device__ __forceinline__ size_t reordered_offset(int b, int col, int dim, int 
 // tile look-up through RA - a dependent load in front of every data load - is done only when
 // the block of rows crosses into another row panel, not per row.
 template <bool BF16, bool REORDER, int VPT>
-__global__ void __launch_bounds__(kNormThreads)
+__global__ void __launch_bounds__(kNormThreads, (VPT <= 2 ? 6 : (VPT <= 4 ? 4 : 2)))
     rmsnorm_kernel(const uint16_t* __restrict__ X, uint16_t* __restrict__ Y,
                    const uint16_t* __restrict__ W, int rows, int dim, int BM, int BN, int rldn,
                    const int* __restrict__ RA, float eps) {
@@ -93,8 +93,9 @@ __global__ void __launch_bounds__(kNormThreads)
     if (j < nvec) wv[i] = *reinterpret_cast<const uint4*>(W + static_cast<size_t>(j) * 8);
   }
 
-  // Element offset of (row 0 of the current panel, this thread's column) per vector.
-  size_t panel_off[VPT];
+  // Offset, in 16-byte vectors, of (row 0 of the current panel, this thread's column) per vector;
+  // 32 bits cover 64 GiB of 16-bit elements.
+  uint32_t panel_off[VPT];
   int panel = -1;
   const size_t ld = REORDER ? static_cast<size_t>(rldn) * BN : static_cast<size_t>(dim);
   auto load_row = [&](int b, uint4 (&dst)[VPT]) {
@@ -105,14 +106,15 @@ __global__ void __launch_bounds__(kNormThreads)
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
           const int j = threadIdx.x + i * kNormThreads;
-          if (j < nvec) panel_off[i] = reordered_offset(pb * BM, j * 8, dim, BM, BN, rldn, RA);
+          if (j < nvec)
+            panel_off[i] = static_cast<uint32_t>(reordered_offset(pb * BM, j * 8, dim, BM, BN, rldn, RA) >> 3);
         }
       }
-      const size_t row_off = static_cast<size_t>(b - pb * BM) * ld;
+      const uint4* row = reinterpret_cast<const uint4*>(X + static_cast<size_t>(b - pb * BM) * ld);
 #pragma unroll
       for (int i = 0; i < VPT; ++i) {
         const int j = threadIdx.x + i * kNormThreads;
-        if (j < nvec) dst[i] = __ldcs(reinterpret_cast<const uint4*>(X + panel_off[i] + row_off));
+        if (j < nvec) dst[i] = __ldcs(row + panel_off[i]);
       }
     } else {
 #pragma unroll
