@@ -132,14 +132,19 @@ FO_DEVICE void prefetch_tmap(const CUtensorMap* m) {
 
 // 2-D tiled load global -> shared, completion counted in bytes on `bar`.
 // c0 is the innermost (contiguous) coordinate; c0 * elem_size must be a multiple of 16 B.
+// `l2_hint` is an L2 eviction-priority policy word (kL2EvictNormal / First / Last).
+constexpr uint64_t kL2EvictNormal = 0x1000000000000000ull;
+constexpr uint64_t kL2EvictFirst = 0x12F0000000000000ull;
+constexpr uint64_t kL2EvictLast = 0x14F0000000000000ull;
+
 FO_DEVICE void tma_load_2d(void* smem_dst, const CUtensorMap* m, uint64_t* bar, int32_t c0,
-                           int32_t c1) {
+                           int32_t c1, uint64_t l2_hint) {
   asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
-      " [%0], [%1, {%3, %4}], [%2];"
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+      " [%0], [%1, {%3, %4}], [%2], %5;"
       :
       : "r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(c0),
-        "r"(c1)
+        "r"(c1), "l"(l2_hint)
       : "memory");
 }
 
@@ -149,13 +154,13 @@ FO_DEVICE void tma_load_2d(void* smem_dst, const CUtensorMap* m, uint64_t* bar, 
 // Each CTA fetches its own operand slice; nothing is broadcast to the peer.
 constexpr uint32_t kPeerBitMask = 0xFEFFFFFFu;
 FO_DEVICE void tma_load_2d_pair(void* smem_dst, const CUtensorMap* m, uint64_t* bar, int32_t c0,
-                                int32_t c1) {
+                                int32_t c1, uint64_t l2_hint) {
   asm volatile(
       "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
-      " [%0], [%1, {%3, %4}], [%2];"
+      ".L2::cache_hint [%0], [%1, {%3, %4}], [%2], %5;"
       :
       : "r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)),
-        "r"(smem_u32(bar) & kPeerBitMask), "r"(c0), "r"(c1)
+        "r"(smem_u32(bar) & kPeerBitMask), "r"(c0), "r"(c1), "l"(l2_hint)
       : "memory");
 }
 

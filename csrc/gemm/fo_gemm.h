@@ -28,6 +28,12 @@ cudaError_t launch_gemm(int algo, bool bf16, bool fused, const GemmTensorMaps& m
                         const GemmParams& p, int grid_x, int nvr, bool cooperative,
                         cudaStream_t stream);
 
+// Sets the L2 eviction priorities of the operand loads for the tiling already in `p`: with
+// column strips swept M-major the B strip is re-read by every wave of the strip (keep it: evict
+// last) while A streams through (evict first); with full row panels it is the other way round.
+// `enable == false` leaves both at normal priority.
+void set_l2_hints(GemmParams* p, bool enable);
+
 int gemm_smem_bytes(int algo);
 
 // Largest grid (CTAs per virtual rank) of this Algo's kernel that is co-resident on the

@@ -139,6 +139,19 @@ std::string prepare_tiling(int algo, GemmParams* p) {
   return "";
 }
 
+void set_l2_hints(GemmParams* p, bool enable) {
+  p->l2_hint_a = ptx::kL2EvictNormal;
+  p->l2_hint_b = ptx::kL2EvictNormal;
+  if (!enable) return;
+  if (p->raster_sw >= p->tiles_n) {
+    p->l2_hint_a = ptx::kL2EvictLast;
+    p->l2_hint_b = ptx::kL2EvictFirst;
+  } else {
+    p->l2_hint_a = ptx::kL2EvictFirst;
+    p->l2_hint_b = ptx::kL2EvictLast;
+  }
+}
+
 int gemm_smem_bytes(int algo) {
   switch (algo & 3) {
     case 0: return GemmSmem<256, 4, false>::kTotalBytes;

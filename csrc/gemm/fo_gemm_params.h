@@ -51,6 +51,8 @@ struct GemmParams {
   uint32_t epoch_done_prev;  // value `done` must have reached before the first push
   uint32_t epoch_done;       // value `done` reaches when this call is complete everywhere
   uint64_t timeout_ns;       // bound for every cross-GPU wait
+  uint64_t l2_hint_a;        // L2 eviction-priority policy of the A / B operand loads
+  uint64_t l2_hint_b;
   const int* RA;             // [num_tiles] natural tile id -> reordered position (nullptr: identity)
   const int* RE;             // [M*N/BN] row remap for kOutScatterRows
   const int* cseg;           // [num_groups] tiles per group (device)

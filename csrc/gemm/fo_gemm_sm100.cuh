@@ -233,13 +233,13 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
           if constexpr (CTA2) {
             // The leader's barrier collects the bytes of both CTAs.
             if (leader) ptx::mbar_arrive_expect_tx(&full_bar[stage], 2 * L::kStageBytes);
-            ptx::tma_load_2d_pair(sa, &maps.a[vr], &full_bar[stage], kb * kBK, tc.m * kBM);
+            ptx::tma_load_2d_pair(sa, &maps.a[vr], &full_bar[stage], kb * kBK, tc.m * kBM, p.l2_hint_a);
             ptx::tma_load_2d_pair(sb, &maps.b[vr], &full_bar[stage], kb * kBK,
-                                  tc.n * BN + static_cast<int>(cta_rank) * L::kBRows);
+                                  tc.n * BN + static_cast<int>(cta_rank) * L::kBRows, p.l2_hint_b);
           } else {
             ptx::mbar_arrive_expect_tx(&full_bar[stage], L::kStageBytes);
-            ptx::tma_load_2d(sa, &maps.a[vr], &full_bar[stage], kb * kBK, tc.m * kBM);
-            ptx::tma_load_2d(sb, &maps.b[vr], &full_bar[stage], kb * kBK, tc.n * BN);
+            ptx::tma_load_2d(sa, &maps.a[vr], &full_bar[stage], kb * kBK, tc.m * kBM, p.l2_hint_a);
+            ptx::tma_load_2d(sb, &maps.b[vr], &full_bar[stage], kb * kBK, tc.n * BN, p.l2_hint_b);
           }
           ++issued;
           if (++stage == STAGES) {

@@ -84,6 +84,7 @@ extern "C" int fo_fused_loopback_noalloc(int comm_op, int ranks, const void* con
   cudaError_t ce = cudaMemsetAsync(control, 0, kControlBytes, stream);
   if (ce != cudaSuccess) return fail(-3, err, err_len, cudaGetErrorString(ce));
 
+  set_l2_hints(&p, false);
   p.out_mode = kOutNatural;
   p.rldn = 1;
   p.comm = comm_op == 0 ? kCommFusedAR : kCommFusedRS;

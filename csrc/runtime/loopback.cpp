@@ -60,6 +60,7 @@ std::vector<int64_t> fused_loopback(std::string comm_op, std::vector<at::Tensor>
   at::Tensor status =
       at::zeros({ws * kStatusWords}, at::TensorOptions().dtype(at::kInt).device(at::kCUDA, dev));
 
+  set_l2_hints(&p, false);
   p.out_mode = natural_out ? kOutNatural : kOutReorder;
   p.rldn = 1;
   p.num_groups = ngroups;

@@ -88,6 +88,8 @@ void OverlapImpl::SetOption(std::string name, int64_t value) {
   } else if (name == "timeout_ms") {
     FO_CHECK(value > 0, "timeout_ms must be positive");
     opt_timeout_ms_ = value;
+  } else if (name == "l2_hints") {
+    opt_l2_hints_ = value ? 1 : 0;
   } else {
     FO_CHECK(false, "unknown option '", name, "'");
   }
@@ -98,6 +100,7 @@ int64_t OverlapImpl::GetOption(std::string name) {
   if (name == "strided_rows") return opt_strided_rows_;
   if (name == "sm_margin") return opt_sm_margin_;
   if (name == "timeout_ms") return opt_timeout_ms_;
+  if (name == "l2_hints") return opt_l2_hints_;
   if (name == "sm_count") return sm_count_;
   if (name == "rank") return rank_;
   if (name == "world") return world_;
@@ -171,6 +174,7 @@ void OverlapImpl::run_plain(const at::Tensor& A, const at::Tensor& B, void* out,
   std::memset(&p, 0, sizeof(p));
   bool bf16 = true;
   setup_problem(algo, A, B, 0, &maps, &p, &bf16);
+  set_l2_hints(&p, opt_l2_hints_ != 0);
   p.out_mode = out_mode;
   p.rldn = rldn < 1 ? 1 : rldn;
   p.signal = signal ? 1 : 0;
@@ -342,6 +346,7 @@ void OverlapImpl::run_fused(int comm, const at::Tensor& A, const at::Tensor& B, 
   }
 
   ++epoch_;
+  set_l2_hints(&p, opt_l2_hints_ != 0);
   p.out_mode = out_mode;
   p.rldn = rldn < 1 ? 1 : rldn;
   p.monitor = monitor ? 1 : 0;
