@@ -247,7 +247,8 @@ def run_ours(args):
     M, N, K = M_AR, N_AR, K_AR_TOTAL // world
     A = (torch.randn(M, K, device=dev) * 0.02).to(torch.bfloat16)
     B = (torch.randn(N, K, device=dev) * 0.02).to(torch.bfloat16)
-    C = impl.symm_empty([M, N], "bfloat16") if world > 1 else torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+    from flashoverlap_b200.parallel import symm
+    C, uses_multicast = symm.alloc_allreduce_output(impl, (M, N), torch.bfloat16, multicast=not args.no_nvls)
 
     state = {}
 
@@ -307,7 +308,7 @@ def run_ours(args):
     t_link = (2.0 * S * (world - 1) / world) / (NVLINK_GBS * 1e9) if world > 1 else 0.0
     roof_ms = max(t_gemm, t_link) * 1e3
 
-    extra = {"algo": algo, "algo_probe_ms": algo_times, "check_max_abs_err": check_err,
+    extra = {"algo": algo, "algo_probe_ms": algo_times, "allreduce_broadcast": "multimem.st (NVLS)" if uses_multicast else "peer stores", "check_max_abs_err": check_err,
              "roofline_ms": round(roof_ms, 4), "roofline_frac": round(roof_ms / ms, 4),
              "roofline_peaks": peaks["source"], "wall_s_timed_region": round(wall, 3)}
 
@@ -450,6 +451,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-extra", action="store_true", help="skip the comparison arms")
+    ap.add_argument("--no-nvls", action="store_true", help="broadcast all-reduce results with peer stores only")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3

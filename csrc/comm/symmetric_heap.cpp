@@ -25,6 +25,7 @@ SymmetricHeap::SymmetricHeap(int rank, int world, ncclComm_t comm, bool loopback
 
 SymmetricHeap::~SymmetricHeap() {
   for (auto& r : regions_) {
+    if (!r->owned) continue;
     for (int i = 0; i < static_cast<int>(r->ptr.size()); ++i) {
       if (r->ptr[i] == nullptr) continue;
       if (r->loopback || i == r->rank) {
@@ -83,6 +84,17 @@ SymmetricRegion* SymmetricHeap::allocate(size_t bytes, cudaStream_t stream) {
   // Nobody may touch a peer's copy before that peer has finished zero-filling it: the
   // all-gather above ran after each rank's memset on the same stream, and every rank has
   // synchronised that stream, so all copies are cleared by now.
+  regions_.push_back(std::move(region));
+  return regions_.back().get();
+}
+
+SymmetricRegion* SymmetricHeap::adopt(size_t bytes, const std::vector<void*>& ptrs, void* multicast) {
+  auto region = std::make_unique<SymmetricRegion>();
+  region->bytes = bytes;
+  region->rank = rank_;
+  region->ptr = ptrs;
+  region->owned = false;
+  region->multicast = multicast;
   regions_.push_back(std::move(region));
   return regions_.back().get();
 }

@@ -25,6 +25,8 @@ struct SymmetricRegion {
   int rank = 0;
   std::vector<void*> ptr;  // ptr[r]: rank r's copy as addressable from this process; ptr[rank] is local
   bool loopback = false;
+  bool owned = true;           // false: registered by the caller, never freed here
+  void* multicast = nullptr;   // NVSwitch multicast mapping of the buffer, if any
   void* local() const { return ptr[rank]; }
   bool contains(const void* p, size_t n) const {
     const char* b = static_cast<const char*>(ptr[rank]);
@@ -43,6 +45,8 @@ class SymmetricHeap {
 
   // Collective.  The memory is zero-filled before any peer can see it.
   SymmetricRegion* allocate(size_t bytes, cudaStream_t stream);
+  // Records a symmetric buffer that somebody else allocated and mapped.
+  SymmetricRegion* adopt(size_t bytes, const std::vector<void*>& ptrs, void* multicast);
   // Region of this heap that fully contains [p, p+n), or nullptr.
   const SymmetricRegion* find(const void* p, size_t n) const;
 

@@ -104,22 +104,33 @@ FO_DEVICE bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
+// Time base of the bounded waits: the SM cycle counter.  Reading %globaltimer costs on the
+// order of a microsecond, which is ruinous inside a hand-off between warps that happens several
+// times per tile; clock64 costs a few cycles.  Timeouts given in nanoseconds are converted
+// with 2 cycles per nanosecond (the SM clock never exceeds 2 GHz), so a wait lasts at least
+// as long as asked and at most about twice as long when the clock is throttled.
+FO_DEVICE uint64_t cycles_now() { return static_cast<uint64_t>(clock64()); }
+FO_DEVICE uint64_t ns_to_cycles(uint64_t ns) { return ns * 2ull; }
+
 // Bounded mbarrier wait.  `abort_flag` is a CTA-shared word any role sets when it gives
 // up, so the other roles leave their own waits promptly instead of each running to
-// its limit.  The bound is wall time (globaltimer), checked every 64 polls; try_wait itself
-// suspends the thread for a short, implementation-defined time.  Returns false on timeout
-// or abort.
+// its limit.  try_wait itself suspends the thread for a short, implementation-defined time;
+// the abort flag and the cycle budget are looked at every 32 polls only.  Returns false on
+// timeout or abort.
 constexpr uint32_t kMbarDrainPolls = 1u << 20;  // poll bound used only while draining at exit
 
 FO_DEVICE bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                  uint64_t timeout_ns) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = globaltimer_ns();
+  for (uint32_t it = 0; it < 32u; ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+  }
+  const uint64_t t0 = cycles_now();
+  const uint64_t budget = ns_to_cycles(timeout_ns);
   for (uint32_t it = 1;; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((it & 63u) == 0u) {
+    if ((it & 31u) == 0u) {
       if (*abort_flag) return false;
-      if (globaltimer_ns() - t0 > timeout_ns) return false;
+      if (cycles_now() - t0 > budget) return false;
     }
   }
 }
@@ -162,6 +173,40 @@ FO_DEVICE void tma_load_2d_pair(void* smem_dst, const CUtensorMap* m, uint64_t* 
       : "r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)),
         "r"(smem_u32(bar) & kPeerBitMask), "r"(c0), "r"(c1), "l"(l2_hint)
       : "memory");
+}
+
+// 2-D tiled store shared -> global (local or peer memory), tracked by this thread's bulk
+// async-group.  The store coordinate x * elem_size must be a multiple of 16 B and neither
+// coordinate may be negative.
+FO_DEVICE void tma_store_2d(const CUtensorMap* m, const void* smem_src, int32_t c0, int32_t c1) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+               :
+               : "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(smem_src)), "r"(c0), "r"(c1)
+               : "memory");
+}
+FO_DEVICE void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// At most N of this thread's most recent bulk groups may still be pending afterwards.
+template <int N>
+FO_DEVICE void bulk_wait_group() {  // writes of older groups are complete
+  asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
+}
+template <int N>
+FO_DEVICE void bulk_wait_group_read() {  // sources of older groups have been read
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+// Orders this thread's generic-proxy shared-memory writes before later async-proxy reads.
+FO_DEVICE void fence_proxy_async_smem() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+FO_DEVICE void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+
+// One store, delivered by the NVSwitch to the same offset of every GPU bound to the multicast
+// object that `mc_addr` maps.
+FO_DEVICE void multimem_st_v4(void* mc_addr, const uint4& v) {
+  asm volatile("multimem.st.weak.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_addr),
+               "f"(__uint_as_float(v.x)), "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)),
+               "f"(__uint_as_float(v.w))
+               : "memory");
 }
 
 // ------------------------------------------------------------------ tcgen05 / TMEM
@@ -314,6 +359,12 @@ FO_DEVICE uint32_t ld_relaxed_sys(const uint32_t* p) {
 FO_DEVICE void red_release_sys_add(uint32_t* p, uint32_t v) {
   asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
+// Relaxed variant: the caller has already issued one release fence for a batch of signals
+// (fence + relaxed atomic is a release pattern); unlike a chain of red.release operations
+// the atomics of a batch do not wait for one another's round trip.
+FO_DEVICE void red_relaxed_sys_add(uint32_t* p, uint32_t v) {
+  asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
 FO_DEVICE void red_release_gpu_add(uint32_t* p, uint32_t v) {
   asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
@@ -350,16 +401,20 @@ FO_DEVICE void report_status(int32_t* status, int32_t code, int32_t a0, int32_t 
 }
 
 // Bounded acquire-spin on a 32-bit counter until it reaches `target` (wrap-safe compare).
-// `timeout_ns` bounds the wait in wall time; returns false when it gives up.
+// `timeout_ns` bounds the wait (see cycles_now); returns false when it gives up.
 template <bool kSysScope>
 FO_DEVICE bool wait_counter_ge(const uint32_t* p, uint32_t target, uint64_t timeout_ns,
                                volatile int* abort_flag, uint32_t* observed) {
-  uint32_t v = kSysScope ? ld_acquire_sys(p) : ld_acquire_gpu(p);
-  if (static_cast<int32_t>(v - target) >= 0) {
-    *observed = v;
-    return true;
+  uint32_t v = 0;
+  for (uint32_t it = 0; it < 16u; ++it) {
+    v = kSysScope ? ld_acquire_sys(p) : ld_acquire_gpu(p);
+    if (static_cast<int32_t>(v - target) >= 0) {
+      *observed = v;
+      return true;
+    }
   }
-  const uint64_t t0 = globaltimer_ns();
+  const uint64_t t0 = cycles_now();
+  const uint64_t budget = ns_to_cycles(timeout_ns);
   uint32_t it = 0;
   while (true) {
     v = kSysScope ? ld_acquire_sys(p) : ld_acquire_gpu(p);
@@ -367,10 +422,10 @@ FO_DEVICE bool wait_counter_ge(const uint32_t* p, uint32_t target, uint64_t time
       *observed = v;
       return true;
     }
-    __nanosleep(64);
+    __nanosleep(32);
     if ((++it & 63u) == 0u) {
       if (abort_flag != nullptr && *abort_flag) break;
-      if (globaltimer_ns() - t0 > timeout_ns) break;
+      if (cycles_now() - t0 > budget) break;
     }
   }
   *observed = v;

@@ -9,7 +9,8 @@ namespace {
 
 __global__ void wait_flag_kernel(int target, int* addr, int group, uint64_t timeout_ns,
                                  int32_t* status) {
-  const uint64_t t0 = ptx::globaltimer_ns();
+  const uint64_t t0 = ptx::cycles_now();
+  const uint64_t budget = ptx::ns_to_cycles(timeout_ns);
   uint32_t it = 0;
   int seen = 0;
   while (true) {
@@ -21,7 +22,7 @@ __global__ void wait_flag_kernel(int target, int* addr, int group, uint64_t time
       return;
     }
     __nanosleep(100);
-    if ((++it & 63u) == 0u && ptx::globaltimer_ns() - t0 > timeout_ns) break;
+    if ((++it & 63u) == 0u && ptx::cycles_now() - t0 > budget) break;
   }
   ptx::report_status(status, kStatusTimeoutWaitKernel, group, seen, target);
 }

@@ -36,6 +36,12 @@ void set_l2_hints(GemmParams* p, bool enable);
 
 int gemm_smem_bytes(int algo);
 
+// Tiles whose pushes the fused kernel keeps in flight before signalling their arrival: with a
+// long main loop (large K) the previous tile's stores are complete by the time the next tile
+// is pushed, with a short one the completion latency of NVLink writes must be covered by
+// letting several tiles overlap.
+inline int default_push_lag(int K) { return K >= 4096 ? 1 : (K >= 2048 ? 2 : 4); }
+
 // Largest grid (CTAs per virtual rank) of this Algo's kernel that is co-resident on the
 // current device: one CTA per SM, or two per schedulable cluster for the CTA-pair kernels.
 // Fused launches must not exceed it, since their CTAs wait for the same CTAs on the peers.

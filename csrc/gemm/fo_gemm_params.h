@@ -32,6 +32,9 @@ enum CommMode : int {
 struct GemmTensorMaps {
   CUtensorMap a[kMaxVirtualRanks];
   CUtensorMap b[kMaxVirtualRanks];
+  // fused kernels: every rank's staging buffer viewed as [ws * tiles * rows_owned, BN], box
+  // (rows_owned x 64): the epilogue's pushes are TMA stores through these
+  CUtensorMap st[kMaxRanks];
 };
 
 struct GemmParams {
@@ -48,6 +51,9 @@ struct GemmParams {
   int ws;            // ranks taking part in the fused collective
   int rank_base;     // rank of virtual rank 0 of this launch
   int strided_rows;  // 1: row i of a tile belongs to rank i % ws (reference), 0: contiguous
+  int diag;          // diagnostic switches (timing studies only): 1 skip the reduction's memory
+                     // traffic, 2 skip the push stores, 4 skip the reducers' flag waits
+  int push_lag;      // tiles whose pushes may be in flight before their arrival is signalled (1..4)
   uint32_t epoch_done_prev;  // value `done` must have reached before the first push
   uint32_t epoch_done;       // value `done` reaches when this call is complete everywhere
   uint64_t timeout_ns;       // bound for every cross-GPU wait
@@ -66,6 +72,7 @@ struct GemmParams {
   uint32_t* flags[kMaxRanks];  // per tile / per group arrival counters
   uint32_t* done[kMaxRanks];   // per-call completion counter
   void* dst[kMaxRanks];        // AllReduce: every rank's output; ReduceScatter: dst[rank] only
+  void* mc_dst;                // AllReduce: multicast mapping of the output (NVLS), or nullptr
 };
 
 // ------------------------------------------------------------------ Algo table

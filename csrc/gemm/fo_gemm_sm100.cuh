@@ -20,7 +20,11 @@
 //               this warp also owns the TMEM allocation (2 accumulators of BN columns);
 //   warps 2-5   epilogue: tcgen05.ld -> convert -> swizzled shared-memory transpose ->
 //               128-byte coalesced global (local or peer) stores, then the signal;
-//   warps 6-9   (fused only) reducer for the row slices this rank owns.
+//   warps 6-9   (fused only) reducer for the row slices this rank owns;
+//   warp 10     (fused only) push: one thread turns every finished shared-memory chunk into TMA
+//               stores to the owning ranks' staging memory and, once a tile's stores have
+//               completed, bumps the owners' arrival counters.  Waiting for remote completion
+//               happens here, off the epilogue's critical path.
 // The two TMEM accumulators let tile i's epilogue run under tile i+1's main loop.
 //
 // CTA2 variant: two CTAs of a cluster (adjacent SMs) share one 256 x 256 tile through
@@ -51,7 +55,7 @@ struct GemmSmem {
   static constexpr int kRingBytes = STAGES * kStageBytes;
   static constexpr int kEpiOffset = kRingBytes;
   static constexpr int kBarOffset = kEpiOffset + 2 * kEpiBufBytes;
-  static constexpr int kNumBars = 2 * STAGES + 4;
+  static constexpr int kNumBars = 2 * STAGES + 4 + 4;  // + chunk_ready[2], chunk_free[2]
   static constexpr int kMiscOffset = kBarOffset + kNumBars * 8;
   static constexpr int kMiscBytes = 64;
   // +1024: the ring is aligned up to 1024 B at run time (128-byte swizzle atom).
@@ -94,6 +98,11 @@ __device__ __forceinline__ void group_of_position(const GemmParams& p, int r, in
   *need = n;
 }
 
+constexpr int kEpilogueThreads = 128;
+constexpr int kReducerThreads = 128;
+constexpr int kThreadsPlain = 64 + kEpilogueThreads;
+constexpr int kThreadsFused = kThreadsPlain + kReducerThreads + 32;  // + push warp
+
 template <bool BF16>
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   if constexpr (BF16) {
@@ -120,10 +129,71 @@ __device__ __forceinline__ void unpack_add(uint32_t w, float& lo, float& hi) {
   }
 }
 
-constexpr int kEpilogueThreads = 128;
-constexpr int kReducerThreads = 128;
-constexpr int kThreadsPlain = 64 + kEpilogueThreads;
-constexpr int kThreadsFused = kThreadsPlain + kReducerThreads;
+
+// Reduction of the row slices this rank owns of one tile: for every 16-byte vector the WS
+// partials are summed in fp32 and the rounded result is written to the output(s).  WS is a
+// template parameter so that the loads of several vectors (about 16 in flight per thread) can
+// be issued before the first sum: the loop is latency bound otherwise.
+template <int BN, bool BF16, int WS>
+__device__ __forceinline__ void reduce_tile(const GemmParams& p, int me, int rt, const uint8_t* src_tile,
+                                            size_t src_stride_bytes, size_t out_base, size_t out_ld) {
+  constexpr int kVecPerRow = BN / 8;
+  constexpr int kRowsOwned = kBM / WS;
+  constexpr int kTotalVec = kRowsOwned * kVecPerRow;
+  constexpr int U = (16 / WS) < 1 ? 1 : (16 / WS);  // vectors per thread per round
+  static_assert(kTotalVec % (kReducerThreads * U) == 0, "tile slice must split evenly over the reducer threads");
+  const bool ar = p.comm == kCommFusedAR;
+  for (int v0 = rt; v0 < kTotalVec; v0 += kReducerThreads * U) {
+    uint4 x[U][WS];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int v = v0 + u * kReducerThreads;
+      const int q = v / kVecPerRow;
+      const int c8 = v - q * kVecPerRow;
+      const uint8_t* sp = src_tile + (static_cast<size_t>(q) * BN + c8 * 8) * 2;
+#pragma unroll
+      for (int s = 0; s < WS; ++s) x[u][s] = ptx::ld_cg_v4(sp + static_cast<size_t>(s) * src_stride_bytes);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int v = v0 + u * kReducerThreads;
+      const int q = v / kVecPerRow;
+      const int c8 = v - q * kVecPerRow;
+      float a[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) a[i] = 0.f;
+#pragma unroll
+      for (int s = 0; s < WS; ++s) {
+        unpack_add<BF16>(x[u][s].x, a[0], a[1]);
+        unpack_add<BF16>(x[u][s].y, a[2], a[3]);
+        unpack_add<BF16>(x[u][s].z, a[4], a[5]);
+        unpack_add<BF16>(x[u][s].w, a[6], a[7]);
+      }
+      uint4 y;
+      y.x = pack2<BF16>(a[0], a[1]);
+      y.y = pack2<BF16>(a[2], a[3]);
+      y.z = pack2<BF16>(a[4], a[5]);
+      y.w = pack2<BF16>(a[6], a[7]);
+      if (ar) {
+        const int lr = p.strided_rows ? (q * WS + me) : (me * kRowsOwned + q);
+        const size_t off = (out_base + static_cast<size_t>(lr) * out_ld + c8 * 8) * 2;
+        if (p.mc_dst != nullptr) {
+          // NVLS: one store, replicated by the switch into every rank's output
+          ptx::multimem_st_v4(reinterpret_cast<uint8_t*>(p.mc_dst) + off, y);
+        } else {
+#pragma unroll
+          for (int d = 0; d < WS; ++d) {
+            const int dd = (me + d) % WS;  // start with the local copy, then fan out
+            ptx::st_v4(reinterpret_cast<uint8_t*>(p.dst[dd]) + off, y);
+          }
+        }
+      } else {
+        const size_t off = (out_base + static_cast<size_t>(q) * out_ld + c8 * 8) * 2;
+        ptx::st_v4(reinterpret_cast<uint8_t*>(p.dst[me]) + off, y);
+      }
+    }
+  }
+}
 
 template <int BN, int STAGES, bool BF16, bool FUSED, bool CTA2>
 __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
@@ -140,6 +210,8 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
   uint64_t* empty_bar = bars + STAGES;
   uint64_t* tmem_full_bar = bars + 2 * STAGES;
   uint64_t* tmem_empty_bar = bars + 2 * STAGES + 2;
+  uint64_t* chunk_ready_bar = bars + 2 * STAGES + 4;  // epilogue -> push warp: chunk written
+  uint64_t* chunk_free_bar = bars + 2 * STAGES + 6;   // push warp -> epilogue: chunk buffer reusable
   uint32_t* misc = reinterpret_cast<uint32_t*>(smem + L::kMiscOffset);
   uint32_t* s_tmem_base = misc;                                   // written by tcgen05.alloc
   volatile int* s_abort = reinterpret_cast<volatile int*>(misc + 1);
@@ -180,6 +252,8 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
       ptx::mbar_init(&tmem_full_bar[i], 1);
       // one arrival per epilogue warp, from both CTAs of a pair
       ptx::mbar_init(&tmem_empty_bar[i], CTA2 ? 8 : 4);
+      ptx::mbar_init(&chunk_ready_bar[i], kEpilogueThreads);
+      ptx::mbar_init(&chunk_free_bar[i], 1);
     }
     *s_abort = 0;
     *s_ep_ok = 1;
@@ -334,7 +408,16 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
     const size_t elem = 2;
     int acc = 0;
     uint32_t acc_phase = 0;
-    bool first_push = true;
+
+    // Fused push: rows are grouped by owning rank in the shared-memory chunk so that each
+    // owner's slice is one contiguous (rows_owned x 128 B) box for a TMA store.
+    int smem_row = my_row;
+    if constexpr (FUSED) {
+      const int o = p.strided_rows ? (my_row % p.ws) : (my_row / rows_owned);
+      const int q = p.strided_rows ? (my_row / p.ws) : (my_row % rows_owned);
+      smem_row = o * rows_owned + q;
+    }
+    uint32_t chunk_no = 0;  // running chunk count: buffer = chunk_no & 1, use count = chunk_no >> 1
 
     // tmem_empty lives in the leader CTA of a pair
     const uint32_t tmem_empty_addr0 =
@@ -351,19 +434,8 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
           ptx::report_status(status, kStatusTimeoutTmemFull, pos, acc, 0);
           *s_abort = 1;
         }
-        if (FUSED && ok && first_push) {
-          // Peers may still be reading the staging slices of the previous call.
-          uint32_t obs;
-          if (!ptx::wait_counter_ge<true>(p.done[me], p.epoch_done_prev, p.timeout_ns, s_abort,
-                                          &obs)) {
-            ptx::report_status(status, kStatusTimeoutStartFlag, me, obs, p.epoch_done_prev);
-            *s_abort = 1;
-            ok = 0;
-          }
-        }
         *s_ep_ok = ok;
       }
-      first_push = false;
       ptx::named_bar_sync(1, kEpilogueThreads);
       if (!*s_ep_ok) break;
       ptx::tc_fence_after_sync();
@@ -374,14 +446,9 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         const int lr = (et >> 3) + 16 * i;
-        size_t off;  // element offset of (row lr, tile column 0)
-        uint8_t* base;
-        if constexpr (FUSED) {
-          const int o = p.strided_rows ? (lr % p.ws) : (lr / rows_owned);
-          const int q = p.strided_rows ? (lr / p.ws) : (lr % rows_owned);
-          base = reinterpret_cast<uint8_t*>(p.stage[o]);
-          off = ((static_cast<size_t>(me) * p.num_tiles + t) * rows_owned + q) * BN;
-        } else {
+        size_t off = 0;  // element offset of (row lr, tile column 0)
+        uint8_t* base = nullptr;
+        if constexpr (!FUSED) {
           base = reinterpret_cast<uint8_t*>(p.out[vr]);
           if (p.out_mode == kOutNatural) {
             off = (static_cast<size_t>(tc.m) * kBM + lr) * p.N + static_cast<size_t>(tc.n) * BN;
@@ -411,7 +478,19 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
           __syncwarp();
           if (lane == 0) ptx::mbar_arrive_cluster(tmem_empty_addr0 + static_cast<uint32_t>(acc) * 8u);
         }
-        uint8_t* buf = epi + (c & 1) * L::kEpiBufBytes + my_row * 128;
+        if constexpr (FUSED) {
+          // The buffer is free once the push warp's stores of its previous use have read it.
+          // A failed wait raises the abort flag but the thread stays in step with the others:
+          // everybody leaves together at the next tile boundary.
+          if (!(p.diag & (8 | 64)) &&
+              !ptx::mbar_wait_bounded(&chunk_free_bar[chunk_no & 1], ((chunk_no >> 1) & 1u) ^ 1u, s_abort,
+                                      pipe_timeout)) {
+            *s_abort = 1;
+          }
+        }
+        const int bsel = FUSED ? static_cast<int>(chunk_no & 1u) : (c & 1);
+        uint8_t* buf = epi + bsel * L::kEpiBufBytes + smem_row * 128;
+        const int sw = smem_row & 7;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           uint4 w;
@@ -419,7 +498,7 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
           w.y = pack2<BF16>(__uint_as_float(v0[8 * j + 2]), __uint_as_float(v0[8 * j + 3]));
           w.z = pack2<BF16>(__uint_as_float(v0[8 * j + 4]), __uint_as_float(v0[8 * j + 5]));
           w.w = pack2<BF16>(__uint_as_float(v0[8 * j + 6]), __uint_as_float(v0[8 * j + 7]));
-          *reinterpret_cast<uint4*>(buf + ((j ^ (my_row & 7)) * 16)) = w;
+          *reinterpret_cast<uint4*>(buf + ((j ^ sw) * 16)) = w;
         }
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -428,29 +507,33 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
           w.y = pack2<BF16>(__uint_as_float(v1[8 * j + 2]), __uint_as_float(v1[8 * j + 3]));
           w.z = pack2<BF16>(__uint_as_float(v1[8 * j + 4]), __uint_as_float(v1[8 * j + 5]));
           w.w = pack2<BF16>(__uint_as_float(v1[8 * j + 6]), __uint_as_float(v1[8 * j + 7]));
-          *reinterpret_cast<uint4*>(buf + (((j + 4) ^ (my_row & 7)) * 16)) = w;
+          *reinterpret_cast<uint4*>(buf + (((j + 4) ^ sw) * 16)) = w;
         }
-        ptx::named_bar_sync(1, kEpilogueThreads);
-        const uint8_t* rbuf = epi + (c & 1) * L::kEpiBufBytes;
+        if constexpr (FUSED) {
+          // Hand the chunk to the push warp (generic-proxy writes ordered before its TMA reads).
+          if (!(p.diag & 8)) {
+            if (!(p.diag & 32)) ptx::fence_proxy_async_smem();
+            ptx::mbar_arrive(&chunk_ready_bar[chunk_no & 1]);
+          }
+          ++chunk_no;
+        } else {
+          ptx::named_bar_sync(1, kEpilogueThreads);
+          const uint8_t* rbuf = epi + (c & 1) * L::kEpiBufBytes;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const int lr = (et >> 3) + 16 * i;
-          const uint4 w =
-              *reinterpret_cast<const uint4*>(rbuf + lr * 128 + (((et & 7) ^ (lr & 7)) * 16));
-          ptx::st_v4(row_ptr[i] + c * 128, w);
+          for (int i = 0; i < 8; ++i) {
+            const int lr = (et >> 3) + 16 * i;
+            const uint4 w =
+                *reinterpret_cast<const uint4*>(rbuf + lr * 128 + (((et & 7) ^ (lr & 7)) * 16));
+            ptx::st_v4(row_ptr[i] + c * 128, w);
+          }
         }
       }
 
-      // All of this tile's stores have been issued by every epilogue thread.
-      ptx::named_bar_sync(1, kEpilogueThreads);
       if constexpr (FUSED) {
-        if (et < p.ws) {
-          int g, need;
-          group_of_position(p, r, &g, &need);
-          ptx::fence_acq_rel_sys();
-          ptx::red_release_sys_add(p.flags[et] + g, 1u);
-        }
+        // arrival counters are bumped by the push warp
       } else {
+        // All of this tile's stores have been issued by every epilogue thread.
+        ptx::named_bar_sync(1, kEpilogueThreads);
         if (et == 0 && p.MM[vr] != nullptr) {
           int* mm = p.MM[vr];
           if (p.signal) {
@@ -473,19 +556,17 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
     }
-  } else {
+  } else if (warp_idx < 10) {
     // ------------------------------------------------------------------ reducer (fused)
     if constexpr (FUSED) {
       const int rt = threadIdx.x - kThreadsPlain;  // 0..127
       const int ws = p.ws;
       const int rows_owned = kBM / ws;
-      constexpr int kVecPerRow = BN / 8;
-      const int total_vec = rows_owned * kVecPerRow;
       const size_t src_stride = static_cast<size_t>(p.num_tiles) * rows_owned * BN;  // elements
       const uint8_t* stage_me = reinterpret_cast<const uint8_t*>(p.stage[me]);
 
       int slot = 0;
-      for (int pos = unit; pos < sched_tiles; pos += num_units, slot ^= 1) {
+      for (int pos = unit; pos < sched_tiles && !(p.diag & 16); pos += num_units, slot ^= 1) {
         const TileCoord tc = my_tile(pos);
         const int t = tc.m * p.tiles_n + tc.n;
         const int r = (p.RA != nullptr) ? p.RA[t] : t;
@@ -493,7 +574,7 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
           int g, need;
           group_of_position(p, r, &g, &need);
           uint32_t obs;
-          const uint32_t target = static_cast<uint32_t>(need * ws);
+          const uint32_t target = (p.diag & 4) ? 0u : static_cast<uint32_t>(need * ws);
           int ok = ptx::wait_counter_ge<true>(p.flags[me] + g, target, p.timeout_ns, s_abort, &obs)
                        ? 1
                        : 0;
@@ -529,37 +610,12 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
         }
         const uint8_t* src_tile = stage_me + static_cast<size_t>(t) * rows_owned * BN * 2;
 
-        for (int v = rt; v < total_vec; v += kReducerThreads) {
-          const int q = v / kVecPerRow;
-          const int c8 = v - q * kVecPerRow;
-          float a[8];
-#pragma unroll
-          for (int i = 0; i < 8; ++i) a[i] = 0.f;
-          const uint8_t* sp = src_tile + (static_cast<size_t>(q) * BN + c8 * 8) * 2;
-#pragma unroll 8
-          for (int s = 0; s < ws; ++s) {
-            const uint4 x = ptx::ld_cg_v4(sp + static_cast<size_t>(s) * src_stride * 2);
-            unpack_add<BF16>(x.x, a[0], a[1]);
-            unpack_add<BF16>(x.y, a[2], a[3]);
-            unpack_add<BF16>(x.z, a[4], a[5]);
-            unpack_add<BF16>(x.w, a[6], a[7]);
-          }
-          uint4 y;
-          y.x = pack2<BF16>(a[0], a[1]);
-          y.y = pack2<BF16>(a[2], a[3]);
-          y.z = pack2<BF16>(a[4], a[5]);
-          y.w = pack2<BF16>(a[6], a[7]);
-          if (p.comm == kCommFusedAR) {
-            const int lr = p.strided_rows ? (q * ws + me) : (me * rows_owned + q);
-            const size_t off = (out_base + static_cast<size_t>(lr) * out_ld + c8 * 8) * 2;
-            for (int d = 0; d < ws; ++d) {
-              const int dd = (me + d) % ws;  // start with the local copy, then fan out
-              ptx::st_v4(reinterpret_cast<uint8_t*>(p.dst[dd]) + off, y);
-            }
-          } else {
-            const size_t off = (out_base + static_cast<size_t>(q) * out_ld + c8 * 8) * 2;
-            ptx::st_v4(reinterpret_cast<uint8_t*>(p.dst[me]) + off, y);
-          }
+        const size_t stride_b = src_stride * 2;
+        if (p.diag & 1) continue;
+        switch (ws) {
+          case 2: reduce_tile<BN, BF16, 2>(p, me, rt, src_tile, stride_b, out_base, out_ld); break;
+          case 4: reduce_tile<BN, BF16, 4>(p, me, rt, src_tile, stride_b, out_base, out_ld); break;
+          default: reduce_tile<BN, BF16, 8>(p, me, rt, src_tile, stride_b, out_base, out_ld); break;
         }
       }
 
@@ -581,7 +637,7 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
         if (rt == 0) {
           *p.local_cnt[vr] = 0u;
           ptx::fence_acq_rel_sys();
-          for (int d = 0; d < ws; ++d) ptx::red_release_sys_add(p.done[(me + d) % ws], 1u);
+          for (int d = 0; d < ws; ++d) ptx::red_relaxed_sys_add(p.done[(me + d) % ws], 1u);
           if (p.comm == kCommFusedAR) {
             uint32_t obs;
             if (!ptx::wait_counter_ge<true>(p.done[me], p.epoch_done, p.timeout_ns, nullptr,
@@ -589,6 +645,88 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
               ptx::report_status(status, kStatusTimeoutDoneFlag, me, obs, p.epoch_done);
             }
           }
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ push warp (fused)
+    if constexpr (FUSED) {
+      if (lane == 0) {
+        constexpr int kChunks = BN / 64;
+        constexpr int kMaxLag = 4;
+        const int rows_owned = kBM / p.ws;
+        const uint8_t* epi = smem + L::kEpiOffset;
+        const int lag = p.push_lag < 1 ? 1 : (p.push_lag > kMaxLag ? kMaxLag : p.push_lag);
+        int ring[kMaxLag];       // wave groups of the tiles whose pushes may still be in flight
+        int ring_head = 0, ring_count = 0;
+        uint32_t chunk_no = 0;
+        bool ok = true;
+
+        auto signal_group = [&](int g) {
+          // The tile's stores have completed (bulk wait); publish that to the owners.
+          // One release fence, then a batch of relaxed atomics that travel concurrently.
+          ptx::fence_proxy_async_all();
+          ptx::fence_acq_rel_sys();
+          for (int o = 0; o < p.ws; ++o) ptx::red_relaxed_sys_add(p.flags[(me + o) % p.ws] + g, 1u);
+        };
+
+        // Peers may still be reading the staging slices of the previous call.
+        {
+          uint32_t obs;
+          if (!ptx::wait_counter_ge<true>(p.done[me], p.epoch_done_prev, p.timeout_ns, s_abort, &obs)) {
+            ptx::report_status(status, kStatusTimeoutStartFlag, me, obs, p.epoch_done_prev);
+            *s_abort = 1;
+            ok = false;
+          }
+        }
+        for (int pos = unit; ok && pos < sched_tiles && !(p.diag & 8); pos += num_units) {
+          const TileCoord tc = my_tile(pos);
+          const int t = tc.m * p.tiles_n + tc.n;
+          const int r = (p.RA != nullptr) ? p.RA[t] : t;
+          const int row0 = (me * p.num_tiles + t) * rows_owned;
+          for (int c = 0; c < kChunks; ++c, ++chunk_no) {
+            const int b = static_cast<int>(chunk_no & 1u);
+            if (!ptx::mbar_wait_bounded(&chunk_ready_bar[b], (chunk_no >> 1) & 1u, s_abort, pipe_timeout)) {
+              ptx::report_status(status, kStatusTimeoutTmemFull, pos, c, 1);
+              *s_abort = 1;
+              ok = false;
+              break;
+            }
+            const uint8_t* cbuf = epi + b * L::kEpiBufBytes;
+            for (int o = 0; o < p.ws && !(p.diag & 2); ++o) {
+              const int oo = (me + o) % p.ws;  // stagger the first target over the peers
+              ptx::tma_store_2d(&maps.st[oo], cbuf + oo * rows_owned * 128, c * 64, row0);
+            }
+            ptx::bulk_commit_group();
+            ptx::bulk_wait_group_read<0>();     // sources read: the epilogue may refill the buffer
+            ptx::mbar_arrive(&chunk_free_bar[b]);
+          }
+          if (!ok) break;
+          int g, need;
+          group_of_position(p, r, &g, &need);
+          if (ring_count == lag) {
+            // The oldest tile in flight was issued `lag` tiles ago; with a main loop between
+            // tiles its stores have long completed and this wait returns at once.
+            switch (lag) {
+              case 1: ptx::bulk_wait_group<kChunks * 1>(); break;
+              case 2: ptx::bulk_wait_group<kChunks * 2>(); break;
+              case 3: ptx::bulk_wait_group<kChunks * 3>(); break;
+              default: ptx::bulk_wait_group<kChunks * 4>(); break;
+            }
+            signal_group(ring[ring_head]);
+            ring_head = (ring_head + 1) % kMaxLag;
+            --ring_count;
+          }
+          ring[(ring_head + ring_count) % kMaxLag] = g;
+          ++ring_count;
+        }
+        // Flush: every push must have landed before it is announced, and no bulk copy may
+        // still read this CTA's shared memory when it exits.
+        ptx::bulk_wait_group<0>();
+        while (ring_count > 0) {
+          signal_group(ring[ring_head]);
+          ring_head = (ring_head + 1) % kMaxLag;
+          --ring_count;
         }
       }
     }

@@ -91,6 +91,7 @@ extern "C" int fo_fused_loopback_noalloc(int comm_op, int ranks, const void* con
   p.ws = ranks;
   p.rank_base = 0;
   p.strided_rows = strided_rows ? 1 : 0;
+  p.push_lag = default_push_lag(K);
   p.epoch_done_prev = 0;
   p.epoch_done = static_cast<uint32_t>(ranks);
   p.timeout_ns = 2000000000ull;
@@ -101,6 +102,12 @@ extern "C" int fo_fused_loopback_noalloc(int comm_op, int ranks, const void* con
     p.flags[r] = reinterpret_cast<uint32_t*>(sig + kSignalFlagsOffset);
     p.status[r] = reinterpret_cast<int32_t*>(control + kStatusOffset) + r * kStatusWords;
     p.stage[r] = staging + r * stage_per_rank;
+    {
+      const std::string e = encode_tmap_16bit(&maps.st[r], p.stage[r],
+                                              static_cast<uint64_t>(ranks) * p.num_tiles * (kBM / ranks), cfg.bn,
+                                              kBM / ranks);
+      if (!e.empty()) return fail(-1, err, err_len, e.c_str());
+    }
     p.dst[r] = out[r];
   }
   cudaDeviceProp prop;

@@ -83,4 +83,13 @@ inline void setup_problem(int algo, const at::Tensor& A, const at::Tensor& B, in
   FO_CHECK(e.empty(), "B: ", e);
 }
 
+// Tensor map over one rank's staging buffer for the epilogue's TMA pushes:
+// [ws * tiles * rows_owned, BN] 16-bit elements, box rows_owned x 64.
+inline void setup_stage_map(GemmTensorMaps* maps, int rank, void* stage, const GemmParams& p, int ws, int bn) {
+  const int rows_owned = kBM / ws;
+  const std::string e = encode_tmap_16bit(&maps->st[rank], stage,
+                                          static_cast<uint64_t>(ws) * p.num_tiles * rows_owned, bn, rows_owned);
+  FO_CHECK(e.empty(), "staging map: ", e);
+}
+
 }  // namespace fo

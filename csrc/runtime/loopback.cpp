@@ -2,6 +2,7 @@
 
 #include <c10/cuda/CUDAGuard.h>
 
+#include <cstdlib>
 #include <cstring>
 
 #include "fused_common.h"
@@ -68,6 +69,8 @@ std::vector<int64_t> fused_loopback(std::string comm_op, std::vector<at::Tensor>
   p.ws = ws;
   p.rank_base = 0;
   p.strided_rows = strided_rows ? 1 : 0;
+  p.push_lag = default_push_lag(p.K);
+  if (const char* d = std::getenv("FLASHOVERLAP_DIAG")) p.diag = std::atoi(d);  // timing studies only
   p.timeout_ns = static_cast<uint64_t>(timeout_ms) * 1000000ull;
   p.RA = int_ptr_or_null(RA, "RA");
   p.cseg = cseg;
@@ -76,6 +79,7 @@ std::vector<int64_t> fused_loopback(std::string comm_op, std::vector<at::Tensor>
     char* sig = static_cast<char*>(signal->ptr[r]);
     p.local_cnt[r] = reinterpret_cast<uint32_t*>(sig + kSignalLocalCntOffset);
     p.stage[r] = stage->ptr[r];
+    setup_stage_map(&maps, r, stage->ptr[r], p, ws, algo_config(static_cast<int>(algo)).bn);
     p.flags[r] = reinterpret_cast<uint32_t*>(sig + kSignalFlagsOffset);
     p.done[r] = reinterpret_cast<uint32_t*>(sig + kSignalDoneOffset);
     p.dst[r] = out[r].data_ptr();

@@ -90,6 +90,11 @@ void OverlapImpl::SetOption(std::string name, int64_t value) {
     opt_timeout_ms_ = value;
   } else if (name == "l2_hints") {
     opt_l2_hints_ = value ? 1 : 0;
+  } else if (name == "nvls") {
+    opt_nvls_ = value ? 1 : 0;
+  } else if (name == "push_lag") {
+    FO_CHECK(value >= 0 && value <= 4, "push_lag must be 0 (automatic) or 1..4");
+    opt_push_lag_ = value;
   } else {
     FO_CHECK(false, "unknown option '", name, "'");
   }
@@ -101,6 +106,8 @@ int64_t OverlapImpl::GetOption(std::string name) {
   if (name == "sm_margin") return opt_sm_margin_;
   if (name == "timeout_ms") return opt_timeout_ms_;
   if (name == "l2_hints") return opt_l2_hints_;
+  if (name == "nvls") return opt_nvls_;
+  if (name == "push_lag") return opt_push_lag_;
   if (name == "sm_count") return sm_count_;
   if (name == "rank") return rank_;
   if (name == "world") return world_;
@@ -132,6 +139,17 @@ at::Tensor OverlapImpl::SymmEmpty(std::vector<int64_t> sizes, std::string dtype)
   // The region belongs to this object; the tensor is a view and must not outlive it.
   return at::from_blob(reg->local(), sizes, [](void*) {},
                        at::TensorOptions().dtype(st).device(at::kCUDA, device_));
+}
+
+void OverlapImpl::RegisterSymmetric(at::Tensor local, std::vector<int64_t> peer_ptrs, int64_t multicast_ptr) {
+  FO_CHECK(heap_ != nullptr, "call nccl_init first");
+  FO_CHECK(local.is_cuda() && local.is_contiguous(), "local must be a contiguous CUDA tensor");
+  FO_CHECK(static_cast<int>(peer_ptrs.size()) == world_, "peer_ptrs must have one address per rank");
+  FO_CHECK(reinterpret_cast<int64_t>(local.data_ptr()) == peer_ptrs[rank_],
+           "peer_ptrs[rank] must be the address of the local tensor");
+  std::vector<void*> ptrs(world_);
+  for (int r = 0; r < world_; ++r) ptrs[r] = reinterpret_cast<void*>(peer_ptrs[r]);
+  heap_->adopt(local.nbytes(), ptrs, reinterpret_cast<void*>(multicast_ptr));
 }
 
 std::vector<int64_t> OverlapImpl::ReadStatus() {
@@ -334,6 +352,7 @@ void OverlapImpl::run_fused(int comm, const at::Tensor& A, const at::Tensor& B, 
     if (reg != nullptr) {
       const size_t off = static_cast<char*>(out.data_ptr()) - static_cast<char*>(reg->local());
       for (int r = 0; r < world_; ++r) p.dst[r] = static_cast<char*>(reg->ptr[r]) + off;
+      if (reg->multicast != nullptr && opt_nvls_ != 0) p.mc_dst = static_cast<char*>(reg->multicast) + off;
     } else {
       // The caller's tensor is ordinary device memory that peers cannot address: reduce into
       // a symmetric buffer and copy.  Allocate outputs with symm_empty to avoid the copy.
@@ -356,6 +375,7 @@ void OverlapImpl::run_fused(int comm, const at::Tensor& A, const at::Tensor& B, 
   p.ws = world_;
   p.rank_base = rank_;
   p.strided_rows = static_cast<int>(opt_strided_rows_);
+  p.push_lag = opt_push_lag_ > 0 ? static_cast<int>(opt_push_lag_) : default_push_lag(p.K);
   p.epoch_done_prev = static_cast<uint32_t>(world_) * (epoch_ - 1);
   p.epoch_done = static_cast<uint32_t>(world_) * epoch_;
   p.timeout_ns = static_cast<uint64_t>(opt_timeout_ms_) * 1000000ull;
@@ -367,6 +387,7 @@ void OverlapImpl::run_fused(int comm, const at::Tensor& A, const at::Tensor& B, 
       reinterpret_cast<uint32_t*>(static_cast<char*>(signal_->local()) + kSignalLocalCntOffset);
   for (int r = 0; r < world_; ++r) {
     p.stage[r] = stage_->ptr[r];
+    setup_stage_map(&maps, r, stage_->ptr[r], p, world_, algo_config(algo).bn);
     char* sig = static_cast<char*>(signal_->ptr[r]);
     p.flags[r] = reinterpret_cast<uint32_t*>(sig + kSignalFlagsOffset);
     p.done[r] = reinterpret_cast<uint32_t*>(sig + kSignalDoneOffset);

@@ -56,12 +56,21 @@ class OverlapImpl : public torch::CustomClassHolder {
   // Options: "mode" (0 fused, 1 gated), "strided_rows" (reduce-scatter row ownership:
   // 1 = rank r owns rows i % world == r as in the reference, 0 = contiguous blocks),
   // "sm_margin" (SMs left to NCCL in gated mode), "timeout_ms" (bound of device waits),
-  // "l2_hints" (1: operand loads carry L2 eviction priorities matched to the tile sweep).
+  // "l2_hints" (1: operand loads carry L2 eviction priorities matched to the tile sweep),
+  // "nvls" (1: broadcast AllReduce results through a registered multicast mapping),
+  // "push_lag" (tiles of pushes kept in flight before their arrival is signalled; 0 = from K).
   void SetOption(std::string name, int64_t value);
   int64_t GetOption(std::string name);
   // Collective allocation of a tensor in symmetric memory.  AllReduce results written into
   // such a tensor need no extra copy.
   at::Tensor SymmEmpty(std::vector<int64_t> sizes, std::string dtype);
+  // Registers symmetric memory allocated elsewhere (for instance by
+  // torch.distributed._symmetric_memory): peer_ptrs[r] is rank r's copy as addressable from
+  // this process, multicast_ptr the NVSwitch multicast mapping of the same buffer or 0.
+  // AllReduce results written into such a tensor are broadcast with one multimem store per
+  // vector (the switch replicates it) instead of one peer store per rank.  The caller keeps
+  // the memory alive for as long as this object may use it.
+  void RegisterSymmetric(at::Tensor local, std::vector<int64_t> peer_ptrs, int64_t multicast_ptr);
   // Status words written by device-side waits that gave up (all zero when healthy).
   std::vector<int64_t> ReadStatus();
   void CheckStatus();  // throws with a description when the status is not ok
@@ -105,6 +114,8 @@ class OverlapImpl : public torch::CustomClassHolder {
   int64_t opt_strided_rows_ = 1;
   int64_t opt_sm_margin_ = 16;
   int64_t opt_timeout_ms_ = 2000;
+  int64_t opt_nvls_ = 1;      // use a registered multicast mapping when there is one
+  int64_t opt_push_lag_ = 0;  // 0: chosen from K
   int64_t opt_l2_hints_ = 0;  // measured: priorities raise DRAM traffic on B200, off by default
 };
 

@@ -1,1 +1,1 @@
-from . import bootstrap, cpu_model, launch  # noqa: F401
+from . import bootstrap, cpu_model, launch, symm  # noqa: F401

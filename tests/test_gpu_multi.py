@@ -68,6 +68,15 @@ def _fused_worker(rank, world):
         C.fill_(float("nan")); torch.cuda.synchronize(); dist.barrier()
         impl.gemm_allreduce_fused(A, B, C, algo)
         res[f"ar_natural_{algo}"] = (C.float() - ref).abs().max().item() / tol
+        # output with an NVSwitch multicast mapping (multimem.st broadcast) when the box offers one
+        from flashoverlap_b200.parallel import symm
+        Cm, used_mc = symm.alloc_allreduce_output(impl, (M, N), torch.bfloat16)
+        for _ in range(2):
+            Cm.fill_(float("nan")); torch.cuda.synchronize(); dist.barrier()
+            impl.gemm_allreduce_fused(A, B, Cm, algo)
+        torch.cuda.synchronize(); dist.barrier()
+        res[f"ar_multicast_{algo}"] = (Cm.float() - ref).abs().max().item() / tol
+        res["info_multicast"] = 1.0 if used_mc else 0.0
         # reduce-scatter, both ownership rules, both layouts
         for strided in (1, 0):
             impl.set_option("strided_rows", strided)
@@ -89,6 +98,7 @@ def test_fused_allreduce_reducescatter_multi_gpu(lib):
     world = _world()
     for r in run_ranks(_fused_worker, world, "nccl"):
         assert r.pop("status") == 0
+        print("multicast output used:", bool(r.pop("info_multicast")))
         for k, v in r.items():
             assert v <= 1.0, (k, v)
 
