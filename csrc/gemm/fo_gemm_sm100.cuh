@@ -482,8 +482,7 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
           // The buffer is free once the push warp's stores of its previous use have read it.
           // A failed wait raises the abort flag but the thread stays in step with the others:
           // everybody leaves together at the next tile boundary.
-          if (!(p.diag & (8 | 64)) &&
-              !ptx::mbar_wait_bounded(&chunk_free_bar[chunk_no & 1], ((chunk_no >> 1) & 1u) ^ 1u, s_abort,
+          if (!ptx::mbar_wait_bounded(&chunk_free_bar[chunk_no & 1], ((chunk_no >> 1) & 1u) ^ 1u, s_abort,
                                       pipe_timeout)) {
             *s_abort = 1;
           }
@@ -511,10 +510,8 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
         }
         if constexpr (FUSED) {
           // Hand the chunk to the push warp (generic-proxy writes ordered before its TMA reads).
-          if (!(p.diag & 8)) {
-            if (!(p.diag & 32)) ptx::fence_proxy_async_smem();
-            ptx::mbar_arrive(&chunk_ready_bar[chunk_no & 1]);
-          }
+          ptx::fence_proxy_async_smem();
+          ptx::mbar_arrive(&chunk_ready_bar[chunk_no & 1]);
           ++chunk_no;
         } else {
           ptx::named_bar_sync(1, kEpilogueThreads);
@@ -566,7 +563,7 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
       const uint8_t* stage_me = reinterpret_cast<const uint8_t*>(p.stage[me]);
 
       int slot = 0;
-      for (int pos = unit; pos < sched_tiles && !(p.diag & 16); pos += num_units, slot ^= 1) {
+      for (int pos = unit; pos < sched_tiles; pos += num_units, slot ^= 1) {
         const TileCoord tc = my_tile(pos);
         const int t = tc.m * p.tiles_n + tc.n;
         const int r = (p.RA != nullptr) ? p.RA[t] : t;
@@ -679,7 +676,7 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
             ok = false;
           }
         }
-        for (int pos = unit; ok && pos < sched_tiles && !(p.diag & 8); pos += num_units) {
+        for (int pos = unit; ok && pos < sched_tiles; pos += num_units) {
           const TileCoord tc = my_tile(pos);
           const int t = tc.m * p.tiles_n + tc.n;
           const int r = (p.RA != nullptr) ? p.RA[t] : t;
