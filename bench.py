@@ -275,7 +275,7 @@ def run_ours(args):
     if os.path.exists(tuned_path) and config.is_tuned(config.load_config(tuned_path)):
         algo, algo_times = int(config.load_config(tuned_path)["Algo"]), None
     else:
-        algo, algo_times = pick_algo(torch, dist, world, step_algo, [1, 17, 5, 0])
+        algo, algo_times = pick_algo(torch, dist, world, step_algo, [19, 3, 17, 1])
 
     sampler = ClockSampler(local) if rank == 0 else None
     ms, clocks, wall = time_steps(torch, dist, world, lambda: step_algo(algo), args.steps, args.warmup, flush, sampler)

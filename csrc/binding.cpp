@@ -125,12 +125,13 @@ void wait_flag(int64_t target, at::Tensor MM, int64_t index, int64_t timeout_ms,
                  "wait_flag");
 }
 
-// Flattened Algo table: for each Algo index (BM, BN, BK, stages, raster strip width, CTA pair).
+// Flattened Algo table: for each Algo index (BM, BN, BK, stages, raster strip width, CTA pair,
+// row halves per CTA).
 std::vector<int64_t> algo_table() {
   std::vector<int64_t> t;
   for (int a = 0; a < fo::kNumAlgos; ++a) {
     const fo::AlgoConfig c = fo::algo_config(a);
-    t.insert(t.end(), {c.bm, c.bn, c.bk, c.stages, c.raster_sw, c.cta2});
+    t.insert(t.end(), {c.bm, c.bn, c.bk, c.stages, c.raster_sw, c.cta2, c.mt});
   }
   return t;
 }

@@ -28,11 +28,11 @@ EncodeFn get_encode_fn() {
 }
 
 // query != nullptr: do not launch, report the largest co-resident grid instead.
-template <int BN, int STAGES, bool BF16, bool FUSED, bool CTA2>
+template <int BN, int STAGES, bool BF16, bool FUSED, bool CTA2, int MT = 1>
 cudaError_t launch_one(const GemmTensorMaps* maps, const GemmParams* p, int grid_x, int nvr,
                        bool cooperative, cudaStream_t stream, int* query) {
-  auto kernel = fo_gemm_kernel<BN, STAGES, BF16, FUSED, CTA2>;
-  constexpr int smem = GemmSmem<BN, STAGES, CTA2>::kTotalBytes;
+  auto kernel = fo_gemm_kernel<BN, STAGES, BF16, FUSED, CTA2, MT>;
+  constexpr int smem = GemmSmem<BN, STAGES, CTA2, MT>::kTotalBytes;
   static bool attr_set[16] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -88,7 +88,7 @@ cudaError_t launch_kernel_index(int kidx, const GemmTensorMaps* maps, const Gemm
     case 0: return launch_one<256, 4, BF16, FUSED, false>(maps, p, grid_x, nvr, coop, s, query);
     case 1: return launch_one<256, 6, BF16, FUSED, true>(maps, p, grid_x, nvr, coop, s, query);
     case 2: return launch_one<128, 6, BF16, FUSED, false>(maps, p, grid_x, nvr, coop, s, query);
-    default: return launch_one<128, 4, BF16, FUSED, false>(maps, p, grid_x, nvr, coop, s, query);
+    default: return launch_one<256, 4, BF16, FUSED, true, 2>(maps, p, grid_x, nvr, coop, s, query);
   }
 }
 
@@ -127,7 +127,9 @@ std::string prepare_tiling(int algo, GemmParams* p) {
   if (algo < 0 || algo >= kNumAlgos) return "Algo index out of range";
   const AlgoConfig c = algo_config(algo);
   if (p->M % c.bm != 0) return "M must be a multiple of 128";
-  if (c.cta2 && p->M % (2 * c.bm) != 0) return "M must be a multiple of 256 for a CTA-pair Algo";
+  if (c.cta2 && p->M % (2 * c.mt * c.bm) != 0)
+    return c.mt == 2 ? "M must be a multiple of 512 for this Algo (CTA pairs, two row halves per CTA)"
+                     : "M must be a multiple of 256 for a CTA-pair Algo";
   if (p->N % c.bn != 0) return "N must be a multiple of the tile width BN of this Algo";
   if (p->K % 8 != 0) return "K must be a multiple of 8";
   p->tiles_m = p->M / c.bm;
@@ -157,7 +159,7 @@ int gemm_smem_bytes(int algo) {
     case 0: return GemmSmem<256, 4, false>::kTotalBytes;
     case 1: return GemmSmem<256, 6, true>::kTotalBytes;
     case 2: return GemmSmem<128, 6, false>::kTotalBytes;
-    default: return GemmSmem<128, 4, false>::kTotalBytes;
+    default: return GemmSmem<256, 4, true, 2>::kTotalBytes;
   }
 }
 

@@ -82,15 +82,17 @@ struct AlgoConfig {
   int stages;
   int raster_sw;  // 0 => full row panels (strip = all N tiles)
   int cta2;       // 1: CTA pairs share 256-row tiles through tcgen05.mma.cta_group::2
+  int mt;         // 128-row halves per CTA (2: a pair covers 512 x 256, accumulators fill TMEM)
 };
 
 constexpr int kNumAlgos = 24;
 
 inline AlgoConfig algo_config(int algo) {
   // algo = raster index * 4 + kernel index
-  static const int kKernelBN[4] = {256, 256, 128, 128};
+  static const int kKernelBN[4] = {256, 256, 128, 256};
   static const int kKernelStages[4] = {4, 6, 6, 4};
-  static const int kKernelCta2[4] = {0, 1, 0, 0};
+  static const int kKernelCta2[4] = {0, 1, 0, 1};
+  static const int kKernelMt[4] = {1, 1, 1, 2};
   static const int kRaster[6] = {8, 4, 2, 1, 16, 0};
   if (algo < 0 || algo >= kNumAlgos) algo = 0;
   AlgoConfig c;
@@ -100,6 +102,7 @@ inline AlgoConfig algo_config(int algo) {
   c.stages = kKernelStages[algo & 3];
   c.raster_sw = kRaster[algo >> 2];
   c.cta2 = kKernelCta2[algo & 3];
+  c.mt = kKernelMt[algo & 3];
   return c;
 }
 

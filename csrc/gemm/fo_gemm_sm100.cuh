@@ -33,6 +33,12 @@
 // accumulators of its own 128 x 256 half, so epilogue, signalling and reducer are unchanged.
 // Halving the B traffic per SM is what lifts the kernel to library-GEMM throughput.
 //
+// MT = 2 (with CTA2): each CTA owns TWO 128-row halves that share its B tile - a 512 x 256 tile
+// per pair, 256 x 256 per CTA.  Operand bytes per FLOP drop by a quarter and the number of
+// waves halves (less DRAM re-reading), which buys clock under the power cap; the price is that
+// the two accumulators fill TMEM, so a tile's epilogue no longer overlaps the next main loop.
+// Worth it when the main loop is long (K per rank in the several thousands).
+//
 // Every wait is bounded: on expiry the role records a status code, raises a CTA-wide abort
 // flag, the producer drains its TMA loads in flight, TMEM is freed and the kernel returns.
 #pragma once
@@ -45,9 +51,10 @@
 
 namespace fo {
 
-template <int BN, int STAGES, bool CTA2 = false>
+template <int BN, int STAGES, bool CTA2 = false, int MT = 1>
 struct GemmSmem {
-  static constexpr int kABytes = kBM * kBK * 2;
+  static constexpr int kAHalfBytes = kBM * kBK * 2;
+  static constexpr int kABytes = MT * kAHalfBytes;
   static constexpr int kBRows = CTA2 ? BN / 2 : BN;  // B rows this CTA loads per k-block
   static constexpr int kBBytes = kBRows * kBK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
@@ -195,11 +202,14 @@ __device__ __forceinline__ void reduce_tile(const GemmParams& p, int me, int rt,
   }
 }
 
-template <int BN, int STAGES, bool BF16, bool FUSED, bool CTA2>
+template <int BN, int STAGES, bool BF16, bool FUSED, bool CTA2, int MT>
 __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
     fo_gemm_kernel(const __grid_constant__ GemmTensorMaps maps,
                    const __grid_constant__ GemmParams p) {
-  using L = GemmSmem<BN, STAGES, CTA2>;
+  static_assert(MT == 1 || (MT == 2 && CTA2 && BN == 256), "two row halves need CTA pairs and BN = 256");
+  using L = GemmSmem<BN, STAGES, CTA2, MT>;
+  // Accumulator slots in TMEM: two tiles in flight (MT = 1) or the two halves of one (MT = 2).
+  constexpr int kAccStages = MT == 2 ? 1 : 2;
   extern __shared__ uint8_t smem_raw[];
   // The ring must start on a 1024-byte boundary of the shared window.
   const uint32_t raw_addr = ptx::smem_u32(smem_raw);
@@ -231,11 +241,12 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
   const bool leader = cta_rank == 0u;
   const int unit = CTA2 ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
   const int num_units = CTA2 ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
-  const int sched_tiles_m = CTA2 ? p.tiles_m / 2 : p.tiles_m;
+  constexpr int kRowsPerUnit = (CTA2 ? 2 : 1) * MT;  // 128-row tiles of one scheduling unit
+  const int sched_tiles_m = p.tiles_m / kRowsPerUnit;
   const int sched_tiles = sched_tiles_m * p.tiles_n;
   auto my_tile = [&](int pos) {
     TileCoord tc = tile_of_position(pos, sched_tiles_m, p.tiles_n, p.raster_sw);
-    if (CTA2) tc.m = 2 * tc.m + static_cast<int>(cta_rank);
+    tc.m = kRowsPerUnit * tc.m + MT * static_cast<int>(cta_rank);  // first half; halves follow
     return tc;
   };
   int32_t* status = p.status[vr];
@@ -307,7 +318,11 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
           if constexpr (CTA2) {
             // The leader's barrier collects the bytes of both CTAs.
             if (leader) ptx::mbar_arrive_expect_tx(&full_bar[stage], 2 * L::kStageBytes);
-            ptx::tma_load_2d_pair(sa, &maps.a[vr], &full_bar[stage], kb * kBK, tc.m * kBM, p.l2_hint_a);
+#pragma unroll
+            for (int h = 0; h < MT; ++h) {
+              ptx::tma_load_2d_pair(sa + h * L::kAHalfBytes, &maps.a[vr], &full_bar[stage], kb * kBK,
+                                    (tc.m + h) * kBM, p.l2_hint_a);
+            }
             ptx::tma_load_2d_pair(sb, &maps.b[vr], &full_bar[stage], kb * kBK,
                                   tc.n * BN + static_cast<int>(cta_rank) * L::kBRows, p.l2_hint_b);
           } else {
@@ -368,9 +383,15 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
           for (int k = 0; k < kBK / 16; ++k) {
             // advance 16 elements (32 B) along K inside the swizzle atom: +2 in 16-byte units
             if constexpr (CTA2) {
-              ptx::umma_f16_ss_pair(tmem_d, da + static_cast<uint64_t>(2 * k),
-                                    db + static_cast<uint64_t>(2 * k), idesc,
-                                    (kb > 0 || k > 0) ? 1u : 0u);
+#pragma unroll
+              for (int h = 0; h < MT; ++h) {
+                // half h: its A rows sit h * 16 KB further in the stage, its accumulator BN
+                // columns further in TMEM; both halves multiply the same B tile
+                ptx::umma_f16_ss_pair(tmem_d + static_cast<uint32_t>(h * BN),
+                                      da + static_cast<uint64_t>(h * (L::kAHalfBytes >> 4) + 2 * k),
+                                      db + static_cast<uint64_t>(2 * k), idesc,
+                                      (kb > 0 || k > 0) ? 1u : 0u);
+              }
             } else {
               ptx::umma_f16_ss(tmem_d, da + static_cast<uint64_t>(2 * k),
                                db + static_cast<uint64_t>(2 * k), idesc,
@@ -394,8 +415,10 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
         } else {
           ptx::umma_commit(&tmem_full_bar[acc]);
         }
-        acc ^= 1;
-        if (acc == 0) acc_phase ^= 1u;
+        if (++acc == kAccStages) {
+          acc = 0;
+          acc_phase ^= 1u;
+        }
       }
     }
   } else if (warp_idx < 6) {
@@ -424,9 +447,7 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
         CTA2 ? ptx::mapa_shared(ptx::smem_u32(&tmem_empty_bar[0]), 0u) : ptx::smem_u32(&tmem_empty_bar[0]);
 
     for (int pos = unit; pos < sched_tiles; pos += num_units) {
-      const TileCoord tc = my_tile(pos);
-      const int t = tc.m * p.tiles_n + tc.n;
-      const int r = (p.RA != nullptr) ? p.RA[t] : t;
+      const TileCoord tc0 = my_tile(pos);
 
       if (et == 0) {
         int ok = ptx::mbar_wait_bounded(&tmem_full_bar[acc], acc_phase, s_abort, pipe_timeout) ? 1 : 0;
@@ -439,6 +460,13 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
       ptx::named_bar_sync(1, kEpilogueThreads);
       if (!*s_ep_ok) break;
       ptx::tc_fence_after_sync();
+
+#pragma unroll 1
+      for (int h = 0; h < MT; ++h) {  // the 128-row halves of this CTA's tile (one unless MT = 2)
+      TileCoord tc = tc0;
+      tc.m += h;
+      const int t = tc.m * p.tiles_n + tc.n;
+      const int r = (p.RA != nullptr) ? p.RA[t] : t;
 
       // Per-thread destinations for the cooperative store phase: thread `et` stores the
       // 16-byte piece (et & 7) of rows (et >> 3) + 16 * i, i = 0..7.
@@ -465,15 +493,15 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
       }
 
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) +
-                             static_cast<uint32_t>(acc * BN);
+                             static_cast<uint32_t>((MT == 2 ? h : acc) * BN);
 #pragma unroll 1
       for (int c = 0; c < BN / 64; ++c) {
         uint32_t v0[32], v1[32];
         ptx::tmem_ld_32x32b_x32(t_row + c * 64, v0);
         ptx::tmem_ld_32x32b_x32(t_row + c * 64 + 32, v1);
         ptx::tmem_ld_wait();
-        if (c == BN / 64 - 1) {
-          // Accumulator fully read by this warp: hand it back to the (leader's) MMA warp.
+        if (c == BN / 64 - 1 && h == MT - 1) {
+          // Accumulator(s) fully read by this warp: hand it back to the (leader's) MMA warp.
           ptx::tc_fence_before_sync();
           __syncwarp();
           if (lane == 0) ptx::mbar_arrive_cluster(tmem_empty_addr0 + static_cast<uint32_t>(acc) * 8u);
@@ -550,8 +578,11 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
         const int order = atomicAdd(mm + p.mm_stride - 1, 1);
         mm[p.mm_stride + r] = order;
       }
-      acc ^= 1;
-      if (acc == 0) acc_phase ^= 1u;
+      }  // halves
+      if (++acc == kAccStages) {
+        acc = 0;
+        acc_phase ^= 1u;
+      }
     }
   } else if (warp_idx < 10) {
     // ------------------------------------------------------------------ reducer (fused)
@@ -563,8 +594,13 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
       const uint8_t* stage_me = reinterpret_cast<const uint8_t*>(p.stage[me]);
 
       int slot = 0;
-      for (int pos = unit; pos < sched_tiles; pos += num_units, slot ^= 1) {
-        const TileCoord tc = my_tile(pos);
+      for (int pos = unit, hh = 0; pos < sched_tiles; slot ^= 1) {
+        TileCoord tc = my_tile(pos);
+        tc.m += hh;  // halves of a unit are reduced one after the other
+        if (++hh == MT) {
+          hh = 0;
+          pos += num_units;
+        }
         const int t = tc.m * p.tiles_n + tc.n;
         const int r = (p.RA != nullptr) ? p.RA[t] : t;
         if (rt == 0) {
@@ -676,8 +712,13 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
             ok = false;
           }
         }
-        for (int pos = unit; ok && pos < sched_tiles; pos += num_units) {
-          const TileCoord tc = my_tile(pos);
+        for (int pos = unit, hh = 0; ok && pos < sched_tiles;) {
+          TileCoord tc = my_tile(pos);
+          tc.m += hh;
+          if (++hh == MT) {
+            hh = 0;
+            pos += num_units;
+          }
           const int t = tc.m * p.tiles_n + tc.n;
           const int r = (p.RA != nullptr) ? p.RA[t] : t;
           const int row0 = (me * p.num_tiles + t) * rows_owned;

@@ -66,7 +66,7 @@ def wait_flag(target: int, counters: torch.Tensor, index: int, timeout_ms: int, 
 
 def algo_table() -> List[Sequence[int]]:
     flat = list(_op().algo_table())
-    return [tuple(flat[i:i + 6]) for i in range(0, len(flat), 6)]
+    return [tuple(flat[i:i + 7]) for i in range(0, len(flat), 7)]
 
 
 def fused_loopback(comm_op: str, A: List[torch.Tensor], B: List[torch.Tensor], out: List[torch.Tensor],

@@ -18,10 +18,11 @@ from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
 
-# (BN, stages, CTA pair) of the four kernels and the raster strips; Algo = raster * 4 + kernel.
+# (BN, stages, CTA pair, row halves per CTA) of the four kernels and the raster strips;
+# Algo = raster * 4 + kernel.
 # Must match algo_config() in csrc/gemm/fo_gemm_params.h (checked against the native table by
 # tests/test_config.py whenever the library is loaded).
-_KERNELS = [(256, 4, 0), (256, 6, 1), (128, 6, 0), (128, 4, 0)]
+_KERNELS = [(256, 4, 0, 1), (256, 6, 1, 1), (128, 6, 0, 1), (256, 4, 1, 2)]
 _RASTERS = [8, 4, 2, 1, 16, 0]
 NUM_ALGOS = len(_KERNELS) * len(_RASTERS)
 BM = 128
@@ -31,8 +32,9 @@ BK = 64
 def algo_params(algo: int) -> Dict[str, int]:
     if not 0 <= algo < NUM_ALGOS:
         raise ValueError(f"Algo {algo} out of range [0, {NUM_ALGOS})")
-    bn, stages, cta2 = _KERNELS[algo & 3]
-    return {"BM": BM, "BN": bn, "BK": BK, "stages": stages, "raster": _RASTERS[algo >> 2], "cta2": cta2}
+    bn, stages, cta2, mt = _KERNELS[algo & 3]
+    return {"BM": BM, "BN": bn, "BK": BK, "stages": stages, "raster": _RASTERS[algo >> 2], "cta2": cta2, "mt": mt,
+            "rows_per_unit": (2 if cta2 else 1) * mt}
 
 
 def algo_tuple(algo: int) -> Tuple[int, ...]:
@@ -40,8 +42,8 @@ def algo_tuple(algo: int) -> Tuple[int, ...]:
     (BM, BN, BK, UMMA_M, UMMA_N, UMMA_K, cta_group, accumulator stages, epilogue chunk,
     pipeline stages, raster strip, split-K)."""
     p = algo_params(algo)
-    return (p["BM"], p["BN"], p["BK"], 128 * (1 + p["cta2"]), p["BN"], 16, 1 + p["cta2"], 2, 64, p["stages"],
-            p["raster"], 1)
+    return (p["BM"] * p["mt"], p["BN"], p["BK"], 128 * (1 + p["cta2"]), p["BN"], 16, 1 + p["cta2"], 3 - p["mt"], 64,
+            p["stages"], p["raster"], 1)
 
 
 def algo_dict() -> Dict[Tuple[int, ...], int]:
@@ -109,11 +111,11 @@ def default_solution(M: int, N: int, algo: int = 0, wave_size: int = 148, groups
     if N % p["BN"]:
         algo = (algo & ~3) | 2
         p = algo_params(algo)
-    if p["cta2"] and M % (2 * p["BM"]):
-        algo = (algo & ~3)
+    if M % (p["rows_per_unit"] * p["BM"]):
+        algo = (algo & ~3) | (1 if M % (2 * p["BM"]) == 0 and N % 256 == 0 else (0 if N % 256 == 0 else 2))
         p = algo_params(algo)
     tiles = (M // p["BM"]) * (N // p["BN"])
-    hint = layout.analytic_hint(M, N, p["BM"], p["BN"], p["raster"], bool(p["cta2"]))
+    hint = layout.analytic_hint(M, N, p["BM"], p["BN"], p["raster"], p["rows_per_unit"])
     nw = layout.div_up(tiles, wave_size)
     cseg = layout.cseg_from_wave_groups(tiles, wave_size, groups or [1] * nw)
     return {"BM": p["BM"], "BN": p["BN"], "dur": 0.0, "Algo": algo, "hint": hint, "cSeg": cseg, "rLDN": 1}

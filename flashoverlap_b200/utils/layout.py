@@ -27,11 +27,12 @@ def div_up(x: int, y: int) -> int:
 
 # ----------------------------------------------------------------------------- tile orders
 
-def raster_order(tiles_m: int, tiles_n: int, strip: int, pair: bool = False) -> List[int]:
+def raster_order(tiles_m: int, tiles_n: int, strip: int, rows_per_unit: int = 1) -> List[int]:
     """Natural tile ids in the order the persistent GEMM visits them.
 
-    ``pair``: the CTA-pair kernels schedule 256-row units; a unit's two 128-row tiles
-    (rows 2i and 2i+1 of the tile grid) are produced together, the even one listed first.
+    ``rows_per_unit``: the CTA-pair kernels schedule units of 2 (or, with two row halves per CTA,
+    4) vertically adjacent 128-row tiles that are produced together; they are listed top to
+    bottom.  ``True`` is accepted for 2.
 
     Tiles are swept in column strips ``strip`` tiles wide, M-major inside a strip
     (``strip <= 0`` or ``>= tiles_n``: full row panels).  Mirrors ``tile_of_position`` in
@@ -40,31 +41,29 @@ def raster_order(tiles_m: int, tiles_n: int, strip: int, pair: bool = False) -> 
     """
     if strip <= 0 or strip > tiles_n:
         strip = tiles_n
-    if pair and tiles_m % 2:
-        raise ValueError("CTA-pair kernels need an even number of tile rows")
+    g = 2 if rows_per_unit is True else max(1, int(rows_per_unit))
+    if tiles_m % g:
+        raise ValueError("the number of tile rows must be a multiple of the rows per scheduling unit")
     order: List[int] = []
-    sched_m = tiles_m // 2 if pair else tiles_m
+    sched_m = tiles_m // g
     for s in range(div_up(tiles_n, strip)):
         w = min(strip, tiles_n - s * strip)
         for m in range(sched_m):
             for j in range(w):
                 n = s * strip + j
-                if pair:
-                    order.append((2 * m) * tiles_n + n)
-                    order.append((2 * m + 1) * tiles_n + n)
-                else:
-                    order.append(m * tiles_n + n)
+                for i in range(g):
+                    order.append((g * m + i) * tiles_n + n)
     return order
 
 
-def analytic_hint(M: int, N: int, BM: int, BN: int, strip: int, pair: bool = False) -> List[int]:
+def analytic_hint(M: int, N: int, BM: int, BN: int, strip: int, rows_per_unit: int = 1) -> List[int]:
     """Completion-order hint of the persistent kernel, known by construction.
 
     CTA c of a grid of G processes positions c, c+G, ... of ``raster_order``; wave w is the
     positions [w*G, (w+1)*G).  The reference has to measure this order with a monitor run
     because its tiles are dispatched by the hardware block scheduler (tune/search.py:83-178).
     """
-    return raster_order(M // BM, N // BN, strip, pair)
+    return raster_order(M // BM, N // BN, strip, rows_per_unit)
 
 
 def reorder_indices(num_tiles: int, hint: Sequence[int], device="cpu") -> torch.Tensor:

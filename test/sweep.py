@@ -53,7 +53,7 @@ def worker(rank, world, args):
                     impl.set_option("timeout_ms", 20000)
                     sm, margin = impl.get_option("sm_count"), impl.get_option("sm_margin")
                     best = None
-                    for algo in ((1, 17) if M % 256 == 0 else (0, 16)):
+                    for algo in ((19, 17, 1) if M % 512 == 0 else ((1, 17) if M % 256 == 0 else (0, 16))):
                         wl = OverlapWorkload(impl, rank, world, M, N, K, algo, comm_op, dt, mode="fused")
                         wl.set_cseg([1] * wl.tiles)
                         t = perf_ms(wl.run, args.warmup, args.reps, args.flush)

@@ -8,10 +8,10 @@ from flashoverlap_b200.utils import config, layout
 
 def test_algo_table_matches_native(lib):
     flat = list(torch.ops.flashoverlap_op.algo_table())
-    assert len(flat) == 6 * config.NUM_ALGOS
+    assert len(flat) == 7 * config.NUM_ALGOS
     for a in range(config.NUM_ALGOS):
         p = config.algo_params(a)
-        assert tuple(flat[6 * a:6 * a + 6]) == (p["BM"], p["BN"], p["BK"], p["stages"], p["raster"], p["cta2"])
+        assert tuple(flat[7 * a:7 * a + 7]) == (p["BM"], p["BN"], p["BK"], p["stages"], p["raster"], p["cta2"], p["mt"])
 
 
 def test_algo_dict_roundtrip(tmp_path):
@@ -41,3 +41,7 @@ def test_default_solution_is_consistent():
     assert sorted(c["hint"]) == list(range(tiles)) and sum(c["cSeg"]) == tiles
     c = config.default_solution(1024, 2048 + 128, algo=0)      # N not a multiple of 256 -> BN 128
     assert c["BN"] == 128 and (c["Algo"] & 3) == 2
+    c = config.default_solution(768, 2048, algo=3)             # M not a multiple of 512 -> plain CTA pairs
+    assert (c["Algo"] & 3) == 1 and sorted(c["hint"]) == list(range((768 // 128) * (2048 // 256)))
+    c = config.default_solution(1024, 2048, algo=7)            # two halves per CTA: units of 4 tile rows
+    assert (c["Algo"] & 3) == 3 and c["hint"][:4] == [0, 8, 16, 24]

@@ -67,11 +67,13 @@ def test_reference_signature_reorder_rmsnorm(cuda):
 
 
 @pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
-@pytest.mark.parametrize("M,N,K,algo", [(128, 256, 64, 0), (256, 512, 320, 1), (384, 384, 192, 2), (128, 128, 1024, 3),
+@pytest.mark.parametrize("M,N,K,algo", [(128, 256, 64, 0), (256, 512, 320, 1), (384, 384, 192, 2), (512, 256, 1024, 3),
                                         (1024, 2048, 512, 4), (2048, 1024, 1000, 8), (1280, 2304, 256, 12),
                                         (1024, 1024, 768, 16), (512, 4096, 128, 20), (2048, 2048, 2048, 6),
                                         (256, 256, 64, 1), (2048, 4096, 1024, 5), (4096, 2048, 512, 9),
-                                        (8192, 8192, 256, 17), (1536, 1280, 384, 21)])
+                                        (8192, 8192, 256, 17), (1536, 1280, 384, 21),
+                                        (512, 512, 64, 3), (2048, 2048, 1024, 7), (4096, 8192, 512, 19),
+                                        (1024, 768, 320, 23)])
 def test_gemm_natural(cuda, impl, dt, M, N, K, algo):
     a, b = _rand((M, K), dt, cuda), _rand((N, K), dt, cuda)
     c = torch.full((M, N), float("nan"), device=cuda, dtype=dt)
@@ -90,7 +92,7 @@ def test_gemm_rejects_bad_shapes(cuda, impl):
         impl.cutlass_gemm(a, b.float(), torch.empty(128, 256, device=cuda, dtype=torch.bfloat16), 0)
 
 
-@pytest.mark.parametrize("algo,rldn", [(0, 1), (6, 1), (0, 2), (1, 1), (5, 2)])
+@pytest.mark.parametrize("algo,rldn", [(0, 1), (6, 1), (0, 2), (1, 1), (5, 2), (3, 1), (7, 2)])
 def test_gemm_reordered_signal_and_monitor(cuda, impl, algo, rldn):
     """World of one: gemm_allreduce_overlap is the reordered GEMM; monitor mode records each
     tile's completion rank exactly once."""
@@ -117,13 +119,14 @@ def test_analytic_hint_matches_monitor(cuda, impl):
     tile at launch position p completes in wave p // grid (checked against the monitor)."""
     _check_hint(cuda, impl, 4)
     _check_hint(cuda, impl, 5)
+    _check_hint(cuda, impl, 7)
 
 
 def _check_hint(cuda, impl, algo):
     M, N, K = 4096, 4096, 512
     p = config.algo_params(algo)
     tm, tn = M // p["BM"], N // p["BN"]
-    hint = layout.analytic_hint(M, N, p["BM"], p["BN"], p["raster"], bool(p["cta2"]))
+    hint = layout.analytic_hint(M, N, p["BM"], p["BN"], p["raster"], p["rows_per_unit"])
     RA = torch.arange(tm * tn, device=cuda, dtype=torch.int32).reshape(tm, tn)   # identity: MM rows = natural ids
     a, b = _rand((M, K), torch.bfloat16, cuda), _rand((N, K), torch.bfloat16, cuda)
     c = torch.empty(M, N, device=cuda, dtype=torch.bfloat16)
@@ -182,7 +185,7 @@ def _loopback_case(cuda, comm_op, ws, M, N, K, algo, strided, natural, repeat=1,
 
 @pytest.mark.parametrize("comm_op", ["all_reduce", "reduce_scatter"])
 @pytest.mark.parametrize("ws,algo,strided,natural", [(2, 0, True, False), (2, 0, False, True), (4, 2, True, True),
-                                                     (4, 3, False, False)])
+                                                     (4, 2, False, False)])
 def test_fused_loopback(cuda, comm_op, ws, algo, strided, natural):
     """All ranks of the fused GEMM+collective kernel in one cooperative launch on one GPU."""
     _loopback_case(cuda, comm_op, ws, 1024, 2048, 512, algo, strided, natural)

@@ -39,7 +39,7 @@ def _fused_worker(rank, world):
     dev = torch.device("cuda", rank)
     impl = _setup(rank, world)
     res = {}
-    for (M, N, K, algo) in ((1024, 2048, 512, 0), (2048, 1024, 256, 6), (2048, 2048, 512, 1)):
+    for (M, N, K, algo) in ((1024, 2048, 512, 0), (2048, 1024, 256, 6), (2048, 2048, 512, 1), (2048, 1024, 256, 3)):
         p = config.algo_params(algo)
         BM, BN = p["BM"], p["BN"]
         tiles = (M // BM) * (N // BN)
@@ -47,7 +47,7 @@ def _fused_worker(rank, world):
         ref = A.float() @ B.float().t()
         dist.all_reduce(ref)
         tol = 0.02 * ref.abs().max().item() + 1e-3
-        hint = layout.analytic_hint(M, N, BM, BN, p["raster"], bool(p["cta2"]))
+        hint = layout.analytic_hint(M, N, BM, BN, p["raster"], p["rows_per_unit"])
         RA = layout.reorder_indices(tiles, hint, device=dev).reshape(M // BM, N // BN)
         mm = torch.zeros(1, N // BN, device=dev, dtype=torch.int32)
         e, eg = torch.empty(0, dtype=torch.int32), torch.empty(0, dtype=torch.int32, device=dev)
@@ -145,7 +145,7 @@ def _api_worker(rank, world):
     # counter-gated NCCL mechanism (the reference's scheme) on both collectives
     impl.set_option("mode", 1)
     wave = impl.get_option("sm_count") - impl.get_option("sm_margin")
-    hint = layout.analytic_hint(M, N, BM, BN, p["raster"], bool(p["cta2"]))
+    hint = layout.analytic_hint(M, N, BM, BN, p["raster"], p["rows_per_unit"])
     cseg = layout.cseg_from_wave_groups(tiles, max(1, min(wave, tiles // 2)), [1] * layout.div_up(tiles, max(1, min(wave, tiles // 2))))
     RA = layout.reorder_indices(tiles, hint, device=dev).reshape(M // BM, N // BN)
     mm = torch.zeros(1, max(N // BN, len(cseg)), device=dev, dtype=torch.int32)

@@ -34,6 +34,16 @@ def test_raster_order_is_strip_major_permutation(tm, tn, strip):
     assert order[: len(first)] == first
 
 
+def test_raster_order_units():
+    # units of 4 vertically adjacent tiles (CTA pairs with two halves each), strips 2 tiles wide
+    order = layout.raster_order(8, 4, 2, rows_per_unit=4)
+    assert sorted(order) == list(range(32))
+    assert order[:8] == [0, 4, 8, 12, 1, 5, 9, 13] and order[8:12] == [16, 20, 24, 28]
+    assert layout.raster_order(4, 2, 2, True) == [0, 2, 1, 3, 4, 6, 5, 7]
+    with pytest.raises(ValueError):
+        layout.raster_order(6, 4, 2, rows_per_unit=4)
+
+
 @pytest.mark.parametrize("rldn", [1, 2])
 def test_reordered_roundtrip_and_addressing(rldn):
     torch.manual_seed(0)

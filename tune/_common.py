@@ -45,7 +45,7 @@ class OverlapWorkload:
         self.BM, self.BN = p["BM"], p["BN"]
         self.M, self.N, self.K = M, N, K
         self.tiles = (M // self.BM) * (N // self.BN)
-        self.hint = hint or layout.analytic_hint(M, N, self.BM, self.BN, p["raster"], bool(p["cta2"]))
+        self.hint = hint or layout.analytic_hint(M, N, self.BM, self.BN, p["raster"], p["rows_per_unit"])
         self.A, self.B = make_operands(M, N, K, dt, dev, seed=rank)
         self.RA = layout.reorder_indices(self.tiles, self.hint, device=dev).reshape(M // self.BM, N // self.BN)
         self.dev, self.dt = dev, dt

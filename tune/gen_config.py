@@ -32,7 +32,8 @@ def candidates_from_csv(path):
     for r in rows[:10]:
         bm, bn, bk = int(r["cta_m"]), int(r["cta_n"]), int(r["cta_k"])
         grp = int(r.get("cta_group", 1) or 1)
-        key = (bm, bn, bk, 128 * grp, bn, 16, grp, 2, 64, int(r["stages"]), int(r["raster"]), 1)
+        acc_stages = 1 if bm == 256 else 2     # 256 rows per CTA: two halves, accumulators fill TMEM
+        key = (bm, bn, bk, 128 * grp, bn, 16, grp, acc_stages, 64, int(r["stages"]), int(r["raster"]), 1)
         if key in table:
             out.append(table[key])
         else:
@@ -60,7 +61,7 @@ def main():
     timed = []
     for algo in algos:
         p = config.algo_params(algo)
-        if args.n % p["BN"] or args.m % (p["BM"] * (2 if p["cta2"] else 1)):
+        if args.n % p["BN"] or args.m % (p["BM"] * p["rows_per_unit"]):
             continue
         timed.append((perf_ms(lambda: impl.cutlass_gemm(A, B, C, algo), WARM_UP, REP, reduce_max=False), algo))
     best = heapq.nsmallest(10, timed)

@@ -34,7 +34,7 @@ def main():
     timed = []
     for algo in range(config.NUM_ALGOS):
         p = config.algo_params(algo)
-        if args.n % p["BN"] or args.m % (p["BM"] * (2 if p["cta2"] else 1)):
+        if args.n % p["BN"] or args.m % (p["BM"] * p["rows_per_unit"]):
             continue
         ms = perf_ms(lambda: impl.cutlass_gemm(A, B, C, algo), WARM_UP, REP, reduce_max=False)
         timed.append((ms, algo))
