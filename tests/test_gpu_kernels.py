@@ -134,7 +134,7 @@ def _check_hint(cuda, impl, algo):
     e = torch.empty(0, dtype=torch.int32)
     impl.gemm_allreduce_overlap(a, b, c, mm, RA, 1, e, e.to(cuda), algo, True)
     order = mm[1:].flatten().cpu()
-    grid = min(impl.get_option("sm_count"), tm * tn)
+    grid = min(impl.get_option("sm_count") * p["mt"], tm * tn)   # tiles finished per wave
     waves_measured = (order // grid)
     waves_analytic = torch.empty(tm * tn, dtype=torch.long)
     waves_analytic[torch.tensor(hint)] = torch.arange(tm * tn) // grid

@@ -59,7 +59,9 @@ def worker(rank, world, args):
         wl = OverlapWorkload(impl, rank, world, args.m, args.n, args.k, algo, args.comm_op, dt, mode=args.mode)
         wave = (sm - margin) if args.mode == "gated" else sm
         if args.verify_hint:
-            log(f"Algo {algo}: hint agreement with monitor = {verify_hint(wl, min(wave, wl.tiles)):.3f}")
+            from flashoverlap_b200.utils import config as _cfg
+            per_wave = wave * _cfg.algo_params(algo)["mt"]       # tiles finished per wave
+            log(f"Algo {algo}: hint agreement with monitor = {verify_hint(wl, min(per_wave, wl.tiles)):.3f}")
         prob = tuner.Problem(args.m, args.n, wl.BM, wl.BN, gemm_ms, sm, world, args.comm_op, sm_margin=margin)
         cands = tuner.candidate_groupings(wl.tiles, wave, max_waves_per_unit=(10 if args.predictive_search else 7))
         if args.mode == "fused":
