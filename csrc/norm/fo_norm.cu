@@ -164,22 +164,39 @@ __global__ void __launch_bounds__(kNormThreads, (VPT <= 2 ? 6 : (VPT <= 4 ? 4 : 
 }
 
 // TO_REORDERED: Y[reordered] = X[natural]; otherwise Y[natural] = X[reordered].
+// Four vectors per thread per round, all loads issued before the first store: the tile look-up
+// through RA is a dependent load in front of every data load, so one vector at a time leaves
+// the memory system idle.
 template <bool TO_REORDERED>
 __global__ void __launch_bounds__(256)
     reorder_kernel(const uint16_t* __restrict__ X, uint16_t* __restrict__ Y, int rows, int dim,
                    int BM, int BN, int rldn, const int* __restrict__ RA) {
+  constexpr int U = 4;
   const int nvec = dim / 8;
   const size_t total = static_cast<size_t>(rows) * nvec;
-  for (size_t v = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; v < total;
-       v += static_cast<size_t>(gridDim.x) * blockDim.x) {
-    const int b = static_cast<int>(v / nvec);
-    const int col = static_cast<int>(v % nvec) * 8;
-    const size_t nat = static_cast<size_t>(b) * dim + col;
-    const size_t reo = reordered_offset(b, col, dim, BM, BN, rldn, RA);
-    if constexpr (TO_REORDERED) {
-      *reinterpret_cast<uint4*>(Y + reo) = __ldcs(reinterpret_cast<const uint4*>(X + nat));
-    } else {
-      *reinterpret_cast<uint4*>(Y + nat) = __ldcs(reinterpret_cast<const uint4*>(X + reo));
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t v0 = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; v0 < total; v0 += stride * U) {
+    size_t src[U], dst[U];
+    uint4 val[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const size_t v = v0 + u * stride;
+      if (v < total) {
+        const int b = static_cast<int>(v / nvec);
+        const int col = static_cast<int>(v % nvec) * 8;
+        const size_t nat = static_cast<size_t>(b) * dim + col;
+        const size_t reo = reordered_offset(b, col, dim, BM, BN, rldn, RA);
+        src[u] = TO_REORDERED ? nat : reo;
+        dst[u] = TO_REORDERED ? reo : nat;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (v0 + u * stride < total) val[u] = __ldcs(reinterpret_cast<const uint4*>(X + src[u]));
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (v0 + u * stride < total) __stcs(reinterpret_cast<uint4*>(Y + dst[u]), val[u]);
     }
   }
 }
