@@ -220,9 +220,3 @@ def run(args, lib_path: str) -> None:
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
-
-
-def bench_unavailable(why: str) -> None:
-    import bench
-    if int(os.environ.get("RANK", "0")) == 0:
-        print(json.dumps({"impl": "reference", "unavailable": why}), file=bench.REAL_STDOUT, flush=True)
