@@ -84,7 +84,9 @@ class OverlapRowParallelLayer(nn.Module):
         # AllReduce results land in symmetric memory so that peers can write them directly.
         self._out = None
         if comm_op == "all_reduce" and world_size > 1 and mode == "fused":
-            self._out = impl.symm_empty([M, out_features], "bfloat16" if dtype == torch.bfloat16 else "float16")
+            # symmetric memory, with an NVSwitch multicast mapping when torch can provide one
+            from ..parallel import symm
+            self._out, self.uses_multicast = symm.alloc_allreduce_output(impl, (M, out_features), dtype)
         self._tmp = None
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:

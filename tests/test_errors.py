@@ -21,3 +21,18 @@ def test_multi_part_messages_raise_cleanly(lib):
     with pytest.raises(RuntimeError, match="16 int64"):
         base = torch.classes.flashoverlap_class.BaselineImpl()
         base.nccl_init(0, 2, [1, 2, 3])
+
+
+def test_symmetric_output_helper_single_rank(lib):
+    """With one rank there is nothing to share: the helper must not touch torch.distributed."""
+    from flashoverlap_b200.parallel import symm
+
+    class OneRank:
+        def get_option(self, name):
+            assert name == "world"
+            return 1
+
+    if not torch.cuda.is_available():
+        pytest.skip("allocates a CUDA tensor")
+    t, mc = symm.alloc_allreduce_output(OneRank(), (4, 8), torch.bfloat16)
+    assert t.shape == (4, 8) and mc is False

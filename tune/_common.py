@@ -50,7 +50,8 @@ class OverlapWorkload:
         self.RA = layout.reorder_indices(self.tiles, self.hint, device=dev).reshape(M // self.BM, N // self.BN)
         self.dev, self.dt = dev, dt
         if comm_op == "all_reduce" and world > 1 and mode == "fused":
-            self.C = impl.symm_empty([M, N], "bfloat16" if dt == torch.bfloat16 else "float16")
+            from flashoverlap_b200.parallel import symm
+            self.C, _ = symm.alloc_allreduce_output(impl, (M, N), dt)
         else:
             self.C = torch.empty(M, N, device=dev, dtype=dt)
         self.D = torch.empty(M // world, N, device=dev, dtype=dt) if comm_op == "reduce_scatter" else None
