@@ -39,6 +39,8 @@ def share_nccl_id(rank: int, world: int) -> List[int]:
     """Rank 0 generates a NCCL unique id; every rank returns the same 16 int64 values."""
     if world == 1:
         return [0] * 16
+    from .._build import load
+    load()   # registers torch.ops.flashoverlap_op
     payload = [torch.ops.flashoverlap_op.generate_nccl_id() if rank == 0 else None]
     dist.broadcast_object_list(payload, src=0)
     return list(payload[0])
