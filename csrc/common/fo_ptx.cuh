@@ -185,6 +185,25 @@ FO_DEVICE void multimem_st_v4(void* mc_addr, const uint4& v) {
                : "memory");
 }
 
+// One load, answered by the NVSwitch with the element-wise sum (accumulated in fp32) of the
+// eight 16-bit values at the same offset of every GPU bound to the multicast object.
+template <bool BF16>
+FO_DEVICE uint4 multimem_ld_reduce_add_v4(const void* mc_addr) {
+  uint4 v;
+  if constexpr (BF16) {
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(mc_addr)
+                 : "memory");
+  } else {
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(mc_addr)
+                 : "memory");
+  }
+  return v;
+}
+
 // ------------------------------------------------------------------ tcgen05 / TMEM
 
 FO_DEVICE void tmem_alloc(uint32_t* smem_dst, uint32_t ncols) {  // whole warp

@@ -33,7 +33,8 @@ struct GemmTensorMaps {
   CUtensorMap a[kMaxVirtualRanks];
   CUtensorMap b[kMaxVirtualRanks];
   // fused kernels: every rank's staging buffer viewed as [ws * tiles * rows_owned, BN], box
-  // (rows_owned x 64): the epilogue's pushes are TMA stores through these
+  // (rows_owned x 64): the epilogue's pushes are TMA stores through these.  Pull variant: this
+  // rank's own staging viewed as [tiles * 128, BN], box (128 x 64).
   CUtensorMap st[kMaxRanks];
 };
 
@@ -68,11 +69,17 @@ struct GemmParams {
   int32_t* status[kMaxVirtualRanks];    // status words
   uint32_t* local_cnt[kMaxVirtualRanks];  // CTAs of this rank that finished reducing
   // indexed by rank (peer-mapped addresses valid on the launching GPU)
-  void* stage[kMaxRanks];      // staging: [src rank][tile][rows owned][BN]
+  void* stage[kMaxRanks];      // staging: [src rank][tile][rows owned][BN] (pull variant: see stage_local)
   uint32_t* flags[kMaxRanks];  // per tile / per group arrival counters
   uint32_t* done[kMaxRanks];   // per-call completion counter
   void* dst[kMaxRanks];        // AllReduce: every rank's output; ReduceScatter: dst[rank] only
   void* mc_dst;                // AllReduce: multicast mapping of the output (NVLS), or nullptr
+  // Pull variant of the fused collective: every rank keeps its partial tiles in its OWN staging
+  // buffer, laid out [tile][owner][rows owned][BN], and the owners fetch them - with one
+  // switch-side reduction per vector when the staging has a multicast mapping (mc_stage), else
+  // with one peer load per rank.
+  int stage_local;
+  void* mc_stage;
 };
 
 // ------------------------------------------------------------------ Algo table

@@ -202,6 +202,94 @@ __device__ __forceinline__ void reduce_tile(const GemmParams& p, int me, int rt,
   }
 }
 
+// Pull variant of the reduction: the partials of the rows this rank owns sit at the same offset
+// `tile_off` (bytes) of EVERY rank's staging buffer.  With a multicast mapping of the staging one
+// multimem.ld_reduce per vector lets the NVSwitch fetch and sum all ranks' copies (fp32
+// accumulation), so only the result crosses this GPU's links; otherwise each vector is loaded
+// from every rank over NVLink and summed here.
+template <int BN, bool BF16, int WS>
+__device__ __forceinline__ void reduce_tile_pull(const GemmParams& p, int me, int rt, size_t tile_off,
+                                                 size_t out_base, size_t out_ld) {
+  constexpr int kVecPerRow = BN / 8;
+  constexpr int kRowsOwned = kBM / WS;
+  constexpr int kTotalVec = kRowsOwned * kVecPerRow;
+  const bool ar = p.comm == kCommFusedAR;
+  const bool sw_reduce = p.mc_stage != nullptr;
+  constexpr int U = (16 / WS) < 1 ? 1 : (16 / WS);  // vectors per thread per round (peer loads)
+  // vectors per thread per round (switch reduction)
+  constexpr int UM = (kTotalVec / kReducerThreads) >= 4 ? 4 : (kTotalVec / kReducerThreads);
+  static_assert(kTotalVec % (kReducerThreads * U) == 0 && kTotalVec % (kReducerThreads * UM) == 0,
+                "tile slice must split evenly over the reducer threads");
+
+  auto store_result = [&](int v, const uint4& y) {
+    const int q = v / kVecPerRow;
+    const int c8 = v - q * kVecPerRow;
+    if (ar) {
+      const int lr = p.strided_rows ? (q * WS + me) : (me * kRowsOwned + q);
+      const size_t off = (out_base + static_cast<size_t>(lr) * out_ld + c8 * 8) * 2;
+      if (p.mc_dst != nullptr) {
+        ptx::multimem_st_v4(reinterpret_cast<uint8_t*>(p.mc_dst) + off, y);
+      } else {
+#pragma unroll
+        for (int d = 0; d < WS; ++d) {
+          const int dd = (me + d) % WS;
+          ptx::st_v4(reinterpret_cast<uint8_t*>(p.dst[dd]) + off, y);
+        }
+      }
+    } else {
+      const size_t off = (out_base + static_cast<size_t>(q) * out_ld + c8 * 8) * 2;
+      ptx::st_v4(reinterpret_cast<uint8_t*>(p.dst[me]) + off, y);
+    }
+  };
+
+  if (sw_reduce) {
+    const uint8_t* mc = reinterpret_cast<const uint8_t*>(p.mc_stage) + tile_off;
+    for (int v0 = rt; v0 < kTotalVec; v0 += kReducerThreads * UM) {
+      uint4 y[UM];
+#pragma unroll
+      for (int u = 0; u < UM; ++u) {
+        // vector v of the slice is its bytes [16 v, 16 v + 16): rows are BN * 2 bytes apart
+        y[u] = ptx::multimem_ld_reduce_add_v4<BF16>(mc + static_cast<size_t>(v0 + u * kReducerThreads) * 16);
+      }
+#pragma unroll
+      for (int u = 0; u < UM; ++u) store_result(v0 + u * kReducerThreads, y[u]);
+    }
+    return;
+  }
+
+  const uint8_t* src[WS];
+#pragma unroll
+  for (int s = 0; s < WS; ++s) src[s] = reinterpret_cast<const uint8_t*>(p.stage[(me + s) % WS]) + tile_off;
+  for (int v0 = rt; v0 < kTotalVec; v0 += kReducerThreads * U) {
+    uint4 x[U][WS];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const size_t voff = static_cast<size_t>(v0 + u * kReducerThreads) * 16;
+#pragma unroll
+      for (int s = 0; s < WS; ++s) x[u][s] = ptx::ld_cg_v4(src[s] + voff);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      float a[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) a[i] = 0.f;
+#pragma unroll
+      for (int s = 0; s < WS; ++s) {
+        unpack_add<BF16>(x[u][s].x, a[0], a[1]);
+        unpack_add<BF16>(x[u][s].y, a[2], a[3]);
+        unpack_add<BF16>(x[u][s].z, a[4], a[5]);
+        unpack_add<BF16>(x[u][s].w, a[6], a[7]);
+      }
+      uint4 y;
+      y.x = pack2<BF16>(a[0], a[1]);
+      y.y = pack2<BF16>(a[2], a[3]);
+      y.z = pack2<BF16>(a[4], a[5]);
+      y.w = pack2<BF16>(a[6], a[7]);
+      store_result(v0 + u * kReducerThreads, y);
+    }
+  }
+}
+
 template <int BN, int STAGES, bool BF16, bool FUSED, bool CTA2, int MT>
 __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
     fo_gemm_kernel(const __grid_constant__ GemmTensorMaps maps,
@@ -645,6 +733,16 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
 
         const size_t stride_b = src_stride * 2;
         if (p.diag & 1) continue;
+        if (p.stage_local) {
+          // rows of owner `me` inside tile t's [owner][rows owned][BN] block of any rank's staging
+          const size_t tile_off = (static_cast<size_t>(t) * kBM + static_cast<size_t>(me) * rows_owned) * BN * 2;
+          switch (ws) {
+            case 2: reduce_tile_pull<BN, BF16, 2>(p, me, rt, tile_off, out_base, out_ld); break;
+            case 4: reduce_tile_pull<BN, BF16, 4>(p, me, rt, tile_off, out_base, out_ld); break;
+            default: reduce_tile_pull<BN, BF16, 8>(p, me, rt, tile_off, out_base, out_ld); break;
+          }
+          continue;
+        }
         switch (ws) {
           case 2: reduce_tile<BN, BF16, 2>(p, me, rt, src_tile, stride_b, out_base, out_ld); break;
           case 4: reduce_tile<BN, BF16, 4>(p, me, rt, src_tile, stride_b, out_base, out_ld); break;
@@ -731,9 +829,14 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
               break;
             }
             const uint8_t* cbuf = epi + b * L::kEpiBufBytes;
-            for (int o = 0; o < p.ws && !(p.diag & 2); ++o) {
-              const int oo = (me + o) % p.ws;  // stagger the first target over the peers
-              ptx::tma_store_2d(&maps.st[oo], cbuf + oo * rows_owned * 128, c * 64, row0);
+            if (p.stage_local) {
+              // pull variant: the whole chunk (rows already grouped by owner) stays on this GPU
+              if (!(p.diag & 2)) ptx::tma_store_2d(&maps.st[me], cbuf, c * 64, t * kBM);
+            } else {
+              for (int o = 0; o < p.ws && !(p.diag & 2); ++o) {
+                const int oo = (me + o) % p.ws;  // stagger the first target over the peers
+                ptx::tma_store_2d(&maps.st[oo], cbuf + oo * rows_owned * 128, c * 64, row0);
+              }
             }
             ptx::bulk_commit_group();
             ptx::bulk_wait_group_read<0>();     // sources read: the epilogue may refill the buffer

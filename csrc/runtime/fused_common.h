@@ -83,12 +83,16 @@ inline void setup_problem(int algo, const at::Tensor& A, const at::Tensor& B, in
   FO_CHECK(e.empty(), "B: ", e);
 }
 
-// Tensor map over one rank's staging buffer for the epilogue's TMA pushes:
-// [ws * tiles * rows_owned, BN] 16-bit elements, box rows_owned x 64.
-inline void setup_stage_map(GemmTensorMaps* maps, int rank, void* stage, const GemmParams& p, int ws, int bn) {
+// Tensor map over one rank's staging buffer for the push warp's TMA stores.
+// Push protocol: [ws * tiles * rows_owned, BN] 16-bit elements, box rows_owned x 64 (one owner's
+// slice of a chunk).  Pull protocol (`stage_local`): [tiles * 128, BN], box 128 x 64 (a whole chunk).
+inline void setup_stage_map(GemmTensorMaps* maps, int rank, void* stage, const GemmParams& p, int ws, int bn,
+                            bool stage_local = false) {
   const int rows_owned = kBM / ws;
-  const std::string e = encode_tmap_16bit(&maps->st[rank], stage,
-                                          static_cast<uint64_t>(ws) * p.num_tiles * rows_owned, bn, rows_owned);
+  const std::string e =
+      stage_local ? encode_tmap_16bit(&maps->st[rank], stage, static_cast<uint64_t>(p.num_tiles) * kBM, bn, kBM)
+                  : encode_tmap_16bit(&maps->st[rank], stage,
+                                      static_cast<uint64_t>(ws) * p.num_tiles * rows_owned, bn, rows_owned);
   FO_CHECK(e.empty(), "staging map: ", e);
 }
 

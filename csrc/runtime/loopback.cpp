@@ -14,7 +14,7 @@ std::vector<int64_t> fused_loopback(std::string comm_op, std::vector<at::Tensor>
                                     c10::optional<at::Tensor> RA_opt,
                                     c10::optional<at::Tensor> cseg_opt, int64_t algo,
                                     bool strided_rows, bool natural_out, int64_t repeat,
-                                    int64_t timeout_ms) {
+                                    int64_t timeout_ms, bool stage_local) {
   const at::Tensor RA = RA_opt.has_value() ? *RA_opt : at::Tensor();
   const at::Tensor cseg_gpu = cseg_opt.has_value() ? *cseg_opt : at::Tensor();
   const int ws = static_cast<int>(A.size());
@@ -70,6 +70,7 @@ std::vector<int64_t> fused_loopback(std::string comm_op, std::vector<at::Tensor>
   p.rank_base = 0;
   p.strided_rows = strided_rows ? 1 : 0;
   p.push_lag = default_push_lag(p.K);
+  p.stage_local = stage_local ? 1 : 0;
   if (const char* d = std::getenv("FLASHOVERLAP_DIAG")) p.diag = std::atoi(d);  // timing studies only
   p.timeout_ns = static_cast<uint64_t>(timeout_ms) * 1000000ull;
   p.RA = int_ptr_or_null(RA, "RA");
@@ -79,7 +80,7 @@ std::vector<int64_t> fused_loopback(std::string comm_op, std::vector<at::Tensor>
     char* sig = static_cast<char*>(signal->ptr[r]);
     p.local_cnt[r] = reinterpret_cast<uint32_t*>(sig + kSignalLocalCntOffset);
     p.stage[r] = stage->ptr[r];
-    setup_stage_map(&maps, r, stage->ptr[r], p, ws, algo_config(static_cast<int>(algo)).bn);
+    setup_stage_map(&maps, r, stage->ptr[r], p, ws, algo_config(static_cast<int>(algo)).bn, stage_local);
     p.flags[r] = reinterpret_cast<uint32_t*>(sig + kSignalFlagsOffset);
     p.done[r] = reinterpret_cast<uint32_t*>(sig + kSignalDoneOffset);
     p.dst[r] = out[r].data_ptr();

@@ -17,12 +17,14 @@ namespace fo {
 // (all_reduce) or [M/ws,N] (reduce_scatter).  RA / cseg_gpu may be None
 // (identity order / one flag per tile).  natural_out selects row-major results instead of
 // the tile-contiguous layout.  The call is repeated `repeat` times back to back to exercise
-// the call-to-call handshake.  Returns ws * kStatusWords status words.
+// the call-to-call handshake.  stage_local selects the pull protocol (partials staged in the
+// producing rank's own memory, owners fetch them; here without a multicast mapping, so with one
+// load per rank).  Returns ws * kStatusWords status words.
 std::vector<int64_t> fused_loopback(std::string comm_op, std::vector<at::Tensor> A,
                                     std::vector<at::Tensor> B, std::vector<at::Tensor> out,
                                     c10::optional<at::Tensor> RA,
                                     c10::optional<at::Tensor> cseg_gpu, int64_t algo,
                                     bool strided_rows, bool natural_out, int64_t repeat,
-                                    int64_t timeout_ms);
+                                    int64_t timeout_ms, bool stage_local);
 
 }  // namespace fo

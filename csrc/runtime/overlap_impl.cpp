@@ -95,6 +95,8 @@ void OverlapImpl::SetOption(std::string name, int64_t value) {
   } else if (name == "push_lag") {
     FO_CHECK(value >= 0 && value <= 4, "push_lag must be 0 (automatic) or 1..4");
     opt_push_lag_ = value;
+  } else if (name == "stage_local") {
+    opt_stage_local_ = value ? 1 : 0;
   } else {
     FO_CHECK(false, "unknown option '", name, "'");
   }
@@ -108,6 +110,7 @@ int64_t OverlapImpl::GetOption(std::string name) {
   if (name == "l2_hints") return opt_l2_hints_;
   if (name == "nvls") return opt_nvls_;
   if (name == "push_lag") return opt_push_lag_;
+  if (name == "stage_local") return opt_stage_local_;
   if (name == "sm_count") return sm_count_;
   if (name == "rank") return rank_;
   if (name == "world") return world_;
@@ -150,6 +153,15 @@ void OverlapImpl::RegisterSymmetric(at::Tensor local, std::vector<int64_t> peer_
   std::vector<void*> ptrs(world_);
   for (int r = 0; r < world_; ++r) ptrs[r] = reinterpret_cast<void*>(peer_ptrs[r]);
   heap_->adopt(local.nbytes(), ptrs, reinterpret_cast<void*>(multicast_ptr));
+}
+
+void OverlapImpl::UseStage(at::Tensor buffer) {
+  FO_CHECK(heap_ != nullptr, "call nccl_init first");
+  FO_CHECK(buffer.is_cuda() && buffer.is_contiguous(), "the staging buffer must be a contiguous CUDA tensor");
+  const SymmetricRegion* reg = heap_->find(buffer.data_ptr(), buffer.nbytes());
+  FO_CHECK(reg != nullptr && reg->local() == buffer.data_ptr(),
+           "use_stage needs a whole symmetric buffer (from symm_empty, or registered with register_symmetric)");
+  user_stage_ = reg;
 }
 
 std::vector<int64_t> OverlapImpl::ReadStatus() {
@@ -320,7 +332,8 @@ void OverlapImpl::ensure_fused_buffers(size_t stage_bytes, size_t nflags) {
   FO_CHECK(heap_ != nullptr, "call nccl_init first");
   FO_CHECK(nflags <= kSignalMaxFlags, "too many tiles/groups for the flag region: ", nflags);
   if (signal_ == nullptr) signal_ = heap_->allocate(kSignalBytes, stream());
-  if (stage_ == nullptr || stage_->bytes < stage_bytes) {
+  const bool user_stage = opt_stage_local_ != 0 && user_stage_ != nullptr && user_stage_->bytes >= stage_bytes;
+  if (!user_stage && (stage_ == nullptr || stage_->bytes < stage_bytes)) {
     // A larger shape than any seen so far: take a new region (the old one stays mapped until
     // this object dies, peers may still hold its address).
     stage_ = heap_->allocate(stage_bytes, stream());
@@ -385,9 +398,16 @@ void OverlapImpl::run_fused(int comm, const at::Tensor& A, const at::Tensor& B, 
   p.status[0] = status_.data_ptr<int>();
   p.local_cnt[0] =
       reinterpret_cast<uint32_t*>(static_cast<char*>(signal_->local()) + kSignalLocalCntOffset);
+  // Pull protocol: partials stay in the producing rank's staging; a staging buffer with a
+  // multicast mapping (use_stage) lets the switch do the summation.
+  const bool pull = opt_stage_local_ != 0;
+  const SymmetricRegion* stage =
+      (pull && user_stage_ != nullptr && user_stage_->bytes >= full_bytes) ? user_stage_ : stage_;
+  p.stage_local = pull ? 1 : 0;
+  if (pull && stage->multicast != nullptr && opt_nvls_ != 0) p.mc_stage = stage->multicast;
   for (int r = 0; r < world_; ++r) {
-    p.stage[r] = stage_->ptr[r];
-    setup_stage_map(&maps, r, stage_->ptr[r], p, world_, algo_config(algo).bn);
+    p.stage[r] = stage->ptr[r];
+    setup_stage_map(&maps, r, stage->ptr[r], p, world_, algo_config(algo).bn, pull);
     char* sig = static_cast<char*>(signal_->ptr[r]);
     p.flags[r] = reinterpret_cast<uint32_t*>(sig + kSignalFlagsOffset);
     p.done[r] = reinterpret_cast<uint32_t*>(sig + kSignalDoneOffset);

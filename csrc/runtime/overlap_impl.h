@@ -58,7 +58,9 @@ class OverlapImpl : public torch::CustomClassHolder {
   // "sm_margin" (SMs left to NCCL in gated mode), "timeout_ms" (bound of device waits),
   // "l2_hints" (1: operand loads carry L2 eviction priorities matched to the tile sweep),
   // "nvls" (1: broadcast AllReduce results through a registered multicast mapping),
-  // "push_lag" (tiles of pushes kept in flight before their arrival is signalled; 0 = from K).
+  // "push_lag" (tiles of pushes kept in flight before their arrival is signalled; 0 = from K),
+  // "stage_local" (1: pull protocol - partials stay in the producing rank's staging buffer and
+  // the owners fetch them, through the switch's reduction when the buffer has a multicast mapping).
   void SetOption(std::string name, int64_t value);
   int64_t GetOption(std::string name);
   // Collective allocation of a tensor in symmetric memory.  AllReduce results written into
@@ -71,6 +73,10 @@ class OverlapImpl : public torch::CustomClassHolder {
   // vector (the switch replicates it) instead of one peer store per rank.  The caller keeps
   // the memory alive for as long as this object may use it.
   void RegisterSymmetric(at::Tensor local, std::vector<int64_t> peer_ptrs, int64_t multicast_ptr);
+  // Staging buffer for the pull protocol (option "stage_local"): a whole symmetric buffer of at
+  // least M*N*2 bytes.  When it carries a multicast mapping the owners' reducers sum the
+  // partials with one switch-side reduction per vector (multimem.ld_reduce).  Same call on every rank.
+  void UseStage(at::Tensor buffer);
   // Status words written by device-side waits that gave up (all zero when healthy).
   std::vector<int64_t> ReadStatus();
   void CheckStatus();  // throws with a description when the status is not ok
@@ -107,6 +113,7 @@ class OverlapImpl : public torch::CustomClassHolder {
   SymmetricRegion* stage_ = nullptr;
   SymmetricRegion* signal_ = nullptr;
   SymmetricRegion* out_ = nullptr;  // symmetric AllReduce output when the caller's is not
+  const SymmetricRegion* user_stage_ = nullptr;  // staging handed in through UseStage
   uint32_t epoch_ = 0;
   at::Tensor status_;  // int32[kStatusWords] on the device
 
@@ -116,6 +123,7 @@ class OverlapImpl : public torch::CustomClassHolder {
   int64_t opt_timeout_ms_ = 2000;
   int64_t opt_nvls_ = 1;      // use a registered multicast mapping when there is one
   int64_t opt_push_lag_ = 0;  // 0: chosen from K
+  int64_t opt_stage_local_ = 0;  // 1: pull protocol (partials staged locally, owners fetch them)
   int64_t opt_l2_hints_ = 0;  // measured: priorities raise DRAM traffic on B200, off by default
 };
 

@@ -72,8 +72,12 @@ def algo_table() -> List[Sequence[int]]:
 def fused_loopback(comm_op: str, A: List[torch.Tensor], B: List[torch.Tensor], out: List[torch.Tensor],
                    RA: Optional[torch.Tensor] = None, cseg: Optional[torch.Tensor] = None, algo: int = 0,
                    strided_rows: bool = True, natural_out: bool = True, repeat: int = 1,
-                   timeout_ms: int = 1000) -> List[List[int]]:
-    """All ranks of a fused GEMM+collective on ONE GPU in one cooperative launch (test aid)."""
+                   timeout_ms: int = 1000, stage_local: bool = False) -> List[List[int]]:
+    """All ranks of a fused GEMM+collective on ONE GPU in one cooperative launch (test aid).
+
+    ``stage_local`` selects the pull protocol: every rank stages its partial tiles in its own
+    memory and the owners fetch them (one load per rank here; one switch-side reduction per
+    vector on a multi-GPU run whose staging has a multicast mapping)."""
     flat = list(_op().fused_loopback(comm_op, A, B, out, RA, cseg, algo, strided_rows, natural_out, repeat,
-                                     timeout_ms))
+                                     timeout_ms, stage_local))
     return [flat[i:i + 8] for i in range(0, len(flat), 8)]

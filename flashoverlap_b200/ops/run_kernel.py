@@ -34,6 +34,8 @@ def main() -> None:
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--dtype", choices=["bf16", "fp16"], default="bf16")
+    ap.add_argument("--stage-local", action="store_true",
+                    help="fused kernels: pull protocol (partials staged locally, owners fetch them)")
     a = ap.parse_args()
 
     dev = torch.device("cuda", 0)
@@ -84,7 +86,7 @@ def main() -> None:
         out = [torch.empty(rows, N, device=dev, dtype=dt) for _ in range(ws)]
         op = "all_reduce" if a.kernel == "fused_ar" else "reduce_scatter"
         flops = 2.0 * M * N * K * ws
-        fn = lambda: ops.fused_loopback(op, A, B, out, algo=a.algo, natural_out=True)
+        fn = lambda: ops.fused_loopback(op, A, B, out, algo=a.algo, natural_out=True, stage_local=a.stage_local)
 
     for _ in range(a.warmup):
         fn()

@@ -1,4 +1,4 @@
-"""Symmetric output buffers for the fused AllReduce.
+"""Symmetric buffers for the fused collectives: AllReduce outputs and pull-protocol staging.
 
 ``alloc_allreduce_output`` returns a tensor that every rank can address.  When
 ``torch.distributed._symmetric_memory`` can provide it, the buffer also carries an NVSwitch
@@ -22,6 +22,23 @@ _keepalive = []
 def alloc_allreduce_output(impl, shape: Sequence[int], dtype=torch.bfloat16, group=None,
                            multicast: bool = True) -> Tuple[torch.Tensor, bool]:
     """Collective.  Returns (tensor, uses_multicast)."""
+    return _alloc(impl, shape, dtype, group, multicast)
+
+
+def alloc_stage(impl, M: int, N: int, dtype=torch.bfloat16, group=None,
+                multicast: bool = True) -> Tuple[torch.Tensor, bool]:
+    """Collective.  Staging buffer for the pull protocol of the fused kernels (option
+    ``stage_local``): [M, N] 16-bit elements per rank, handed to the runtime with ``use_stage``.
+    With a multicast mapping the owners' reducers fetch the sum of all ranks' partials with one
+    ``multimem.ld_reduce`` per vector - the NVSwitch does the addition and only the result crosses
+    the owner's links.  Returns (tensor, uses_multicast)."""
+    t, mc = _alloc(impl, (M, N), dtype, group, multicast)
+    if impl.get_option("world") > 1:
+        impl.use_stage(t)
+    return t, mc
+
+
+def _alloc(impl, shape, dtype, group, multicast):
     world = impl.get_option("world")
     if world == 1:
         return torch.empty(*shape, dtype=dtype, device="cuda"), False

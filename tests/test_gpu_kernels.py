@@ -159,7 +159,8 @@ def test_wait_flag_completes_and_times_out(cuda):
     assert torch.ones(4, device=cuda).sum().item() == 4
 
 
-def _loopback_case(cuda, comm_op, ws, M, N, K, algo, strided, natural, repeat=1, groups=None, dt=torch.bfloat16):
+def _loopback_case(cuda, comm_op, ws, M, N, K, algo, strided, natural, repeat=1, groups=None, dt=torch.bfloat16,
+                   stage_local=False):
     p = config.algo_params(algo)
     BM, BN = p["BM"], p["BN"]
     tiles = (M // BM) * (N // BN)
@@ -171,7 +172,7 @@ def _loopback_case(cuda, comm_op, ws, M, N, K, algo, strided, natural, repeat=1,
     rows = M if comm_op == "all_reduce" else M // ws
     out = [torch.full((rows, N), float("nan"), device=cuda, dtype=dt) for _ in range(ws)]
     st = ops.fused_loopback(comm_op, A, B, out, RA=RA, cseg=cseg, algo=algo, strided_rows=strided,
-                            natural_out=natural, repeat=repeat, timeout_ms=2000)
+                            natural_out=natural, repeat=repeat, timeout_ms=2000, stage_local=stage_local)
     assert all(s[0] == 0 for s in st), st
     for r in range(ws):
         if comm_op == "all_reduce":
@@ -189,6 +190,17 @@ def _loopback_case(cuda, comm_op, ws, M, N, K, algo, strided, natural, repeat=1,
 def test_fused_loopback(cuda, comm_op, ws, algo, strided, natural):
     """All ranks of the fused GEMM+collective kernel in one cooperative launch on one GPU."""
     _loopback_case(cuda, comm_op, ws, 1024, 2048, 512, algo, strided, natural)
+
+
+@pytest.mark.parametrize("comm_op", ["all_reduce", "reduce_scatter"])
+def test_fused_loopback_pull_protocol(cuda, comm_op):
+    """Partials staged in the producing rank's own buffer, owners fetch and sum them."""
+    _loopback_case(cuda, comm_op, 2, 1024, 2048, 512, 0, True, True, stage_local=True)
+    _loopback_case(cuda, comm_op, 4, 1024, 2048, 256, 2, False, False, repeat=2, stage_local=True)
+    _loopback_case(cuda, comm_op, 8, 2048, 2048, 256, 0, True, False, repeat=2, stage_local=True)
+    _loopback_case(cuda, comm_op, 8, 1024, 1024, 128, 2, False, True, stage_local=True)
+    _loopback_case(cuda, comm_op, 2, 2048, 2048, 256, 0, True, False, repeat=3, groups=[40, 50, 38],
+                   dt=torch.float16, stage_local=True)
 
 
 def test_fused_loopback_eight_ranks(cuda):

@@ -103,6 +103,56 @@ def test_fused_allreduce_reducescatter_multi_gpu(lib):
             assert v <= 1.0, (k, v)
 
 
+def _pull_worker(rank, world):
+    """Pull protocol: partials staged in the producing rank's memory, owners fetch them."""
+    from flashoverlap_b200.parallel import symm
+    from flashoverlap_b200.utils import config, layout
+    dev = torch.device("cuda", rank)
+    impl = _setup(rank, world)
+    impl.set_option("stage_local", 1)
+    switch_reduce = os.environ.get("FLASHOVERLAP_TEST_SWITCH_REDUCE", "0") == "1"
+    res = {"info_switch_reduce": 0.0}
+    for (M, N, K, algo) in ((1024, 2048, 512, 0), (2048, 2048, 512, 1), (2048, 1024, 256, 3)):
+        BM = config.algo_params(algo)["BM"]
+        A, B = _rand((M, K), dev, 30 + rank), _rand((N, K), dev, 40 + rank)
+        ref = A.float() @ B.float().t()
+        dist.all_reduce(ref)
+        tol = 0.02 * ref.abs().max().item() + 1e-3
+        stagings = ["peer_loads"] + (["switch"] if switch_reduce else [])
+        for how in stagings:
+            if how == "switch":
+                _, used = symm.alloc_stage(impl, M, N, torch.bfloat16)   # multimem.ld_reduce when `used`
+                res["info_switch_reduce"] = 1.0 if used else 0.0
+            C, _ = symm.alloc_allreduce_output(impl, (M, N), torch.bfloat16)
+            for _ in range(3):
+                C.fill_(float("nan")); torch.cuda.synchronize(); dist.barrier()
+                impl.gemm_allreduce_fused(A, B, C, algo)
+            torch.cuda.synchronize(); dist.barrier()
+            res[f"ar_{how}_{algo}"] = (C.float() - ref).abs().max().item() / tol
+            for strided in (1, 0):
+                impl.set_option("strided_rows", strided)
+                rows = layout.owned_rows(M, BM, world, rank, bool(strided)).to(dev)
+                D = torch.full((M // world, N), float("nan"), device=dev, dtype=torch.bfloat16)
+                for _ in range(2):
+                    impl.gemm_reducescatter_fused(A, B, D, algo)
+                torch.cuda.synchronize(); dist.barrier()
+                res[f"rs_{how}_{algo}_{strided}"] = (D.float() - ref[rows]).abs().max().item() / tol
+            impl.set_option("strided_rows", 1)
+    res["status"] = impl.read_status()[0]
+    return res
+
+
+def test_pull_protocol_multi_gpu(lib):
+    """Set FLASHOVERLAP_TEST_SWITCH_REDUCE=1 to also stage in multicast-mapped memory, where the
+    owners' reducers sum with multimem.ld_reduce."""
+    world = _world()
+    for r in run_ranks(_pull_worker, world, "nccl"):
+        assert r.pop("status") == 0
+        print("switch-side reduction used:", bool(r.pop("info_switch_reduce")))
+        for k, v in r.items():
+            assert v <= 1.0, (k, v)
+
+
 def _api_worker(rank, world):
     from flashoverlap_b200 import ops
     from flashoverlap_b200.parallel import bootstrap
