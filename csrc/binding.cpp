@@ -136,6 +136,24 @@ std::vector<int64_t> algo_table() {
   return t;
 }
 
+// Row tables of the fused all-to-all for one rank: row_end[8], dst_row[8], rows sent, rows
+// received (see all2all_plan in runtime/fused_common.h).  Host only.
+std::vector<int64_t> all2all_plan(at::Tensor mLen_CPU, int64_t rank) {
+  FO_CHECK(!mLen_CPU.is_cuda() && mLen_CPU.scalar_type() == at::kInt && mLen_CPU.is_contiguous() &&
+               mLen_CPU.dim() == 2 && mLen_CPU.size(0) == mLen_CPU.size(1) &&
+               mLen_CPU.size(0) <= fo::kMaxRanks,
+           "mLen_CPU must be a contiguous square int32 host tensor of at most 8 x 8");
+  const int ws = static_cast<int>(mLen_CPU.size(0));
+  FO_CHECK(rank >= 0 && rank < ws, "rank out of range");
+  const fo::All2AllPlan plan = fo::all2all_plan(mLen_CPU.data_ptr<int>(), ws, static_cast<int>(rank));
+  std::vector<int64_t> out;
+  for (int d = 0; d < fo::kMaxRanks; ++d) out.push_back(plan.row_end[d]);
+  for (int d = 0; d < fo::kMaxRanks; ++d) out.push_back(plan.dst_row[d]);
+  out.push_back(plan.send_rows);
+  out.push_back(plan.recv_rows);
+  return out;
+}
+
 }  // namespace
 
 TORCH_LIBRARY(flashoverlap_class, m) {
@@ -168,6 +186,7 @@ TORCH_LIBRARY(flashoverlap_class, m) {
       // additions
       .def("gemm_allreduce_fused", &OverlapImpl::GemmAllReduceFused)
       .def("gemm_reducescatter_fused", &OverlapImpl::GemmReduceScatterFused)
+      .def("gemm_all2all_fused", &OverlapImpl::GemmAll2AllFused)
       .def("set_option", &OverlapImpl::SetOption)
       .def("get_option", &OverlapImpl::GetOption)
       .def("symm_empty", &OverlapImpl::SymmEmpty)
@@ -189,4 +208,5 @@ TORCH_LIBRARY(flashoverlap_op, m) {
   m.def("wait_flag", &wait_flag);
   m.def("algo_table", &algo_table);
   m.def("fused_loopback", &fo::fused_loopback);
+  m.def("all2all_plan", &all2all_plan);
 }

@@ -6,6 +6,9 @@
 
 namespace fo {
 
+// Both blocks travel as kernel parameters; stay inside the classic 4 KB parameter space.
+static_assert(sizeof(GemmTensorMaps) + sizeof(GemmParams) <= 4096, "kernel parameters exceed 4 KB");
+
 namespace {
 
 using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -28,10 +31,10 @@ EncodeFn get_encode_fn() {
 }
 
 // query != nullptr: do not launch, report the largest co-resident grid instead.
-template <int BN, int STAGES, bool BF16, bool FUSED, bool CTA2, int MT = 1>
+template <int BN, int STAGES, bool BF16, bool FUSED, bool CTA2, int MT = 1, bool A2A = false>
 cudaError_t launch_one(const GemmTensorMaps* maps, const GemmParams* p, int grid_x, int nvr,
                        bool cooperative, cudaStream_t stream, int* query) {
-  auto kernel = fo_gemm_kernel<BN, STAGES, BF16, FUSED, CTA2, MT>;
+  auto kernel = fo_gemm_kernel<BN, STAGES, BF16, FUSED, CTA2, MT, A2A>;
   constexpr int smem = GemmSmem<BN, STAGES, CTA2, MT>::kTotalBytes;
   static bool attr_set[16] = {};
   int dev = 0;
@@ -81,20 +84,24 @@ cudaError_t launch_one(const GemmTensorMaps* maps, const GemmParams* p, int grid
   return cudaLaunchKernelEx(&cfg, kernel, *maps, *p);
 }
 
-template <bool BF16, bool FUSED>
+template <bool BF16, bool FUSED, bool A2A = false>
 cudaError_t launch_kernel_index(int kidx, const GemmTensorMaps* maps, const GemmParams* p,
                                 int grid_x, int nvr, bool coop, cudaStream_t s, int* query) {
   switch (kidx) {
-    case 0: return launch_one<256, 4, BF16, FUSED, false>(maps, p, grid_x, nvr, coop, s, query);
-    case 1: return launch_one<256, 6, BF16, FUSED, true>(maps, p, grid_x, nvr, coop, s, query);
-    case 2: return launch_one<128, 6, BF16, FUSED, false>(maps, p, grid_x, nvr, coop, s, query);
-    default: return launch_one<256, 4, BF16, FUSED, true, 2>(maps, p, grid_x, nvr, coop, s, query);
+    case 0: return launch_one<256, 4, BF16, FUSED, false, 1, A2A>(maps, p, grid_x, nvr, coop, s, query);
+    case 1: return launch_one<256, 6, BF16, FUSED, true, 1, A2A>(maps, p, grid_x, nvr, coop, s, query);
+    case 2: return launch_one<128, 6, BF16, FUSED, false, 1, A2A>(maps, p, grid_x, nvr, coop, s, query);
+    default: return launch_one<256, 4, BF16, FUSED, true, 2, A2A>(maps, p, grid_x, nvr, coop, s, query);
   }
 }
 
 cudaError_t dispatch(int algo, bool bf16, bool fused, const GemmTensorMaps* maps, const GemmParams* p,
                      int grid_x, int nvr, bool coop, cudaStream_t s, int* query) {
   const int kidx = algo & 3;
+  if (p != nullptr && p->comm == kCommFusedA2A) {
+    if (bf16) return launch_kernel_index<true, false, true>(kidx, maps, p, grid_x, nvr, coop, s, query);
+    return launch_kernel_index<false, false, true>(kidx, maps, p, grid_x, nvr, coop, s, query);
+  }
   if (bf16) {
     if (fused) return launch_kernel_index<true, true>(kidx, maps, p, grid_x, nvr, coop, s, query);
     return launch_kernel_index<true, false>(kidx, maps, p, grid_x, nvr, coop, s, query);

@@ -18,12 +18,14 @@ enum OutMode : int {
   kOutNatural = 0,      // row-major [M, N]
   kOutReorder = 1,      // tile-contiguous, tile t at position RA[t] (reference layout)
   kOutScatterRows = 2,  // reorder + per-row remap through RE (reduce-scatter staging layout)
+  kOutAll2All = 3,      // row m goes to the rank and row that a2a_tab assigns to it (all-to-all kernels)
 };
 
 enum CommMode : int {
   kCommNone = 0,
   kCommFusedAR = 2,
   kCommFusedRS = 3,
+  kCommFusedA2A = 4,  // rows of C stored straight into the destination ranks' receive buffers
 };
 
 // One tensor map per virtual rank.  A launch normally carries one rank (gridDim.y == 1);
@@ -80,6 +82,14 @@ struct GemmParams {
   // with one peer load per rank.
   int stage_local;
   void* mc_stage;
+  // All-to-all kernels: [virtual rank][2][kMaxRanks] ints on the device.  Row 0: end (exclusive)
+  // of the run of C rows bound for each rank, runs packed in rank order; row 1: the row of that
+  // rank's receive buffer where this rank's run starts.  C rows past the last run go nowhere.
+  const int* a2a_tab;
+  // All-to-all kernels: ready[r] counts the ranks that have entered the current call (their
+  // receive buffers may be overwritten from then on); nobody stores before it reaches epoch_ready.
+  uint32_t* ready[kMaxRanks];
+  uint32_t epoch_ready;
 };
 
 // ------------------------------------------------------------------ Algo table

@@ -290,11 +290,12 @@ __device__ __forceinline__ void reduce_tile_pull(const GemmParams& p, int me, in
   }
 }
 
-template <int BN, int STAGES, bool BF16, bool FUSED, bool CTA2, int MT>
+template <int BN, int STAGES, bool BF16, bool FUSED, bool CTA2, int MT, bool A2A = false>
 __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
     fo_gemm_kernel(const __grid_constant__ GemmTensorMaps maps,
                    const __grid_constant__ GemmParams p) {
   static_assert(MT == 1 || (MT == 2 && CTA2 && BN == 256), "two row halves need CTA pairs and BN = 256");
+  static_assert(!(A2A && FUSED), "the all-to-all epilogue is a variant of the plain kernel");
   using L = GemmSmem<BN, STAGES, CTA2, MT>;
   // Accumulator slots in TMEM: two tiles in flight (MT = 1) or the two halves of one (MT = 2).
   constexpr int kAccStages = MT == 2 ? 1 : 2;
@@ -534,7 +535,31 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
     const uint32_t tmem_empty_addr0 =
         CTA2 ? ptx::mapa_shared(ptx::smem_u32(&tmem_empty_bar[0]), 0u) : ptx::smem_u32(&tmem_empty_bar[0]);
 
-    for (int pos = unit; pos < sched_tiles; pos += num_units) {
+    bool go = true;
+    if constexpr (A2A) {
+      // Start-of-call handshake of the all-to-all: a rank's receive buffer may be overwritten
+      // only after that rank has entered this call (its readers of the previous call's rows
+      // come earlier in its stream).  CTA 0 announces this rank; every CTA waits, before its
+      // first store, until all ranks have announced themselves.  The main loop runs meanwhile.
+      if (et == 0) {
+        if (blockIdx.x == 0) {
+          ptx::fence_acq_rel_sys();
+          for (int d = 0; d < p.ws; ++d) ptx::red_relaxed_sys_add(p.ready[(me + d) % p.ws], 1u);
+        }
+        uint32_t obs;
+        int ok = ptx::wait_counter_ge<true>(p.ready[me], p.epoch_ready, p.timeout_ns, s_abort, &obs) ? 1 : 0;
+        if (!ok) {
+          ptx::report_status(status, kStatusTimeoutStartFlag, me, obs, p.epoch_ready);
+          *s_abort = 1;
+        }
+        *s_ep_ok = ok;
+      }
+      ptx::named_bar_sync(1, kEpilogueThreads);
+      go = *s_ep_ok != 0;
+      ptx::named_bar_sync(1, kEpilogueThreads);  // everybody has read the verdict before it is reused
+    }
+
+    for (int pos = unit; go && pos < sched_tiles; pos += num_units) {
       const TileCoord tc0 = my_tile(pos);
 
       if (et == 0) {
@@ -559,12 +584,31 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
       // Per-thread destinations for the cooperative store phase: thread `et` stores the
       // 16-byte piece (et & 7) of rows (et >> 3) + 16 * i, i = 0..7.
       uint8_t* row_ptr[8];
+      uint32_t row_valid = 0xffu;  // all-to-all: bit i clear = row i has no destination
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         const int lr = (et >> 3) + 16 * i;
         size_t off = 0;  // element offset of (row lr, tile column 0)
         uint8_t* base = nullptr;
-        if constexpr (!FUSED) {
+        if constexpr (A2A) {
+          // Row m of C belongs to the run of the first rank whose run ends after it.
+          const int m = tc.m * kBM + lr;
+          const int* tab = p.a2a_tab + vr * 2 * kMaxRanks;
+          int d = 0, start = 0;
+          while (d < p.ws) {
+            const int end = __ldg(tab + d);
+            if (m < end) break;
+            start = end;
+            ++d;
+          }
+          if (d < p.ws) {
+            base = reinterpret_cast<uint8_t*>(p.dst[d]);
+            off = (static_cast<size_t>(__ldg(tab + kMaxRanks + d)) + static_cast<size_t>(m - start)) * p.N +
+                  static_cast<size_t>(tc.n) * BN;
+          } else {
+            row_valid &= ~(1u << i);
+          }
+        } else if constexpr (!FUSED) {
           base = reinterpret_cast<uint8_t*>(p.out[vr]);
           if (p.out_mode == kOutNatural) {
             off = (static_cast<size_t>(tc.m) * kBM + lr) * p.N + static_cast<size_t>(tc.n) * BN;
@@ -637,7 +681,7 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
             const int lr = (et >> 3) + 16 * i;
             const uint4 w =
                 *reinterpret_cast<const uint4*>(rbuf + lr * 128 + (((et & 7) ^ (lr & 7)) * 16));
-            ptx::st_v4(row_ptr[i] + c * 128, w);
+            if (!A2A || ((row_valid >> i) & 1u)) ptx::st_v4(row_ptr[i] + c * 128, w);
           }
         }
       }
@@ -670,6 +714,25 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
       if (++acc == kAccStages) {
         acc = 0;
         acc_phase ^= 1u;
+      }
+    }
+    if constexpr (A2A) {
+      // End-of-call handshake of the all-to-all: once every CTA of this rank has issued its
+      // stores, the last one tells every rank that this rank's rows have been sent and waits
+      // until every rank has said the same - this rank's receive buffer is then complete.
+      ptx::named_bar_sync(1, kEpilogueThreads);
+      if (et == 0) {
+        ptx::fence_acq_rel_sys();
+        const uint32_t old = atomicAdd(p.local_cnt[vr], 1u);
+        if (old == gridDim.x - 1) {
+          *p.local_cnt[vr] = 0u;
+          ptx::fence_acq_rel_sys();
+          for (int d = 0; d < p.ws; ++d) ptx::red_relaxed_sys_add(p.done[(me + d) % p.ws], 1u);
+          uint32_t obs;
+          if (!ptx::wait_counter_ge<true>(p.done[me], p.epoch_done, p.timeout_ns, nullptr, &obs)) {
+            ptx::report_status(status, kStatusTimeoutDoneFlag, me, obs, p.epoch_done);
+          }
+        }
       }
     }
   } else if (warp_idx < 10) {

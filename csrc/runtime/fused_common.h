@@ -18,6 +18,7 @@ namespace fo {
 // that remote atomics on one never contend with local atomics on the other.
 constexpr size_t kSignalDoneOffset = 0;
 constexpr size_t kSignalLocalCntOffset = 128;
+constexpr size_t kSignalReadyOffset = 256;  // all-to-all: ranks that have entered the current call
 constexpr size_t kSignalFlagsOffset = 1024;
 constexpr size_t kSignalMaxFlags = 65536;
 constexpr size_t kSignalBytes = kSignalFlagsOffset + kSignalMaxFlags * sizeof(uint32_t);
@@ -94,6 +95,39 @@ inline void setup_stage_map(GemmTensorMaps* maps, int rank, void* stage, const G
                   : encode_tmap_16bit(&maps->st[rank], stage,
                                       static_cast<uint64_t>(ws) * p.num_tiles * rows_owned, bn, rows_owned);
   FO_CHECK(e.empty(), "staging map: ", e);
+}
+
+// Send/receive plan of the variable-size all-to-all on packed rows for rank `me`
+// (reference semantics, src/overlap_impl.cu:181-212): mlen is the row-major [ws, ws] matrix of
+// row counts, rank r sends mlen[r][i] rows to rank i, the runs for the other ranks are packed in
+// rank order in C, the runs received from the other ranks are packed in rank order in D, and a
+// rank's own run is part of neither.
+struct All2AllPlan {
+  int row_end[kMaxRanks];  // end (exclusive) of the run of C rows bound for each rank
+  int dst_row[kMaxRanks];  // first row of that rank's D that this rank's run lands on
+  int64_t send_rows;       // C rows that go anywhere
+  int64_t recv_rows;       // D rows that arrive here
+};
+
+inline All2AllPlan all2all_plan(const int* mlen, int ws, int me) {
+  All2AllPlan plan;
+  int64_t acc = 0;
+  for (int d = 0; d < kMaxRanks; ++d) {
+    if (d < ws && d != me) acc += mlen[me * ws + d];
+    FO_CHECK(acc < (1ll << 31), "all-to-all row counts overflow 32 bits");
+    plan.row_end[d] = static_cast<int>(acc);
+    int64_t before = 0;
+    for (int j = 0; j < me && d < ws; ++j) {
+      if (j != d) before += mlen[j * ws + d];
+    }
+    plan.dst_row[d] = static_cast<int>(before);
+  }
+  plan.send_rows = acc;
+  plan.recv_rows = 0;
+  for (int j = 0; j < ws; ++j) {
+    if (j != me) plan.recv_rows += mlen[j * ws + me];
+  }
+  return plan;
 }
 
 }  // namespace fo

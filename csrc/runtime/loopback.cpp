@@ -14,7 +14,8 @@ std::vector<int64_t> fused_loopback(std::string comm_op, std::vector<at::Tensor>
                                     c10::optional<at::Tensor> RA_opt,
                                     c10::optional<at::Tensor> cseg_opt, int64_t algo,
                                     bool strided_rows, bool natural_out, int64_t repeat,
-                                    int64_t timeout_ms, bool stage_local) {
+                                    int64_t timeout_ms, bool stage_local,
+                                    c10::optional<at::Tensor> mlen_opt) {
   const at::Tensor RA = RA_opt.has_value() ? *RA_opt : at::Tensor();
   const at::Tensor cseg_gpu = cseg_opt.has_value() ? *cseg_opt : at::Tensor();
   const int ws = static_cast<int>(A.size());
@@ -27,8 +28,10 @@ std::vector<int64_t> fused_loopback(std::string comm_op, std::vector<at::Tensor>
     comm = kCommFusedAR;
   } else if (comm_op == "reduce_scatter") {
     comm = kCommFusedRS;
+  } else if (comm_op == "all_to_all") {
+    comm = kCommFusedA2A;
   } else {
-    FO_CHECK(false, "comm_op must be 'all_reduce' or 'reduce_scatter'");
+    FO_CHECK(false, "comm_op must be 'all_reduce', 'reduce_scatter' or 'all_to_all'");
     comm = kCommFusedAR;
   }
   c10::cuda::CUDAGuard guard(A[0].device());
@@ -51,12 +54,33 @@ std::vector<int64_t> fused_loopback(std::string comm_op, std::vector<at::Tensor>
   const size_t nflags = ngroups > 0 ? ngroups : p.num_tiles;
   FO_CHECK(nflags <= kSignalMaxFlags, "too many flags");
   const size_t full_bytes = static_cast<size_t>(p.M) * p.N * 2;
-  const int64_t out_elems = comm == kCommFusedAR ? static_cast<int64_t>(p.M) * p.N
-                                                 : static_cast<int64_t>(p.M) * p.N / ws;
-  for (int r = 0; r < ws; ++r) check_out(out[r], A[r], out_elems, "out");
+  const bool a2a = comm == kCommFusedA2A;
+  at::Tensor tab;  // all-to-all row tables of every virtual rank
+  if (a2a) {
+    FO_CHECK(mlen_opt.has_value(), "all_to_all needs mlen");
+    const at::Tensor& mlen = *mlen_opt;
+    FO_CHECK(!mlen.is_cuda() && mlen.scalar_type() == at::kInt && mlen.is_contiguous() &&
+                 mlen.numel() == static_cast<int64_t>(ws) * ws,
+             "mlen must be a contiguous int32 host tensor of shape [ranks, ranks]");
+    at::Tensor host = at::zeros({ws * 2 * kMaxRanks}, at::TensorOptions().dtype(at::kInt));
+    for (int r = 0; r < ws; ++r) {
+      const All2AllPlan plan = all2all_plan(mlen.data_ptr<int>(), ws, r);
+      FO_CHECK(plan.send_rows <= p.M, "mlen sends more rows than A has");
+      check_out(out[r], A[r], plan.recv_rows * p.N, "out");
+      for (int d = 0; d < kMaxRanks; ++d) {
+        host.data_ptr<int>()[(r * 2 + 0) * kMaxRanks + d] = plan.row_end[d];
+        host.data_ptr<int>()[(r * 2 + 1) * kMaxRanks + d] = plan.dst_row[d];
+      }
+    }
+    tab = host.to(at::Device(at::kCUDA, dev));
+  } else {
+    const int64_t out_elems = comm == kCommFusedAR ? static_cast<int64_t>(p.M) * p.N
+                                                   : static_cast<int64_t>(p.M) * p.N / ws;
+    for (int r = 0; r < ws; ++r) check_out(out[r], A[r], out_elems, "out");
+  }
 
   SymmetricHeap heap(0, ws, nullptr, /*loopback=*/true);
-  SymmetricRegion* stage = heap.allocate(full_bytes, stream);
+  SymmetricRegion* stage = heap.allocate(a2a ? 256 : full_bytes, stream);
   SymmetricRegion* signal = heap.allocate(kSignalBytes, stream);
   at::Tensor status =
       at::zeros({ws * kStatusWords}, at::TensorOptions().dtype(at::kInt).device(at::kCUDA, dev));
@@ -71,6 +95,10 @@ std::vector<int64_t> fused_loopback(std::string comm_op, std::vector<at::Tensor>
   p.strided_rows = strided_rows ? 1 : 0;
   p.push_lag = default_push_lag(p.K);
   p.stage_local = stage_local ? 1 : 0;
+  if (a2a) {
+    p.out_mode = kOutAll2All;
+    p.a2a_tab = tab.data_ptr<int>();
+  }
   if (const char* d = std::getenv("FLASHOVERLAP_DIAG")) p.diag = std::atoi(d);  // timing studies only
   p.timeout_ns = static_cast<uint64_t>(timeout_ms) * 1000000ull;
   p.RA = int_ptr_or_null(RA, "RA");
@@ -83,13 +111,15 @@ std::vector<int64_t> fused_loopback(std::string comm_op, std::vector<at::Tensor>
     setup_stage_map(&maps, r, stage->ptr[r], p, ws, algo_config(static_cast<int>(algo)).bn, stage_local);
     p.flags[r] = reinterpret_cast<uint32_t*>(sig + kSignalFlagsOffset);
     p.done[r] = reinterpret_cast<uint32_t*>(sig + kSignalDoneOffset);
+    p.ready[r] = reinterpret_cast<uint32_t*>(sig + kSignalReadyOffset);
     p.dst[r] = out[r].data_ptr();
   }
   const int per_rank = std::max(1, std::min(prop.multiProcessorCount / ws, p.num_tiles));
   for (int64_t it = 1; it <= repeat; ++it) {
     p.epoch_done_prev = static_cast<uint32_t>(ws) * static_cast<uint32_t>(it - 1);
     p.epoch_done = static_cast<uint32_t>(ws) * static_cast<uint32_t>(it);
-    cuda_check(launch_gemm(static_cast<int>(algo), bf16, true, maps, p, per_rank, ws,
+    p.epoch_ready = p.epoch_done;
+    cuda_check(launch_gemm(static_cast<int>(algo), bf16, /*fused=*/!a2a, maps, p, per_rank, ws,
                            /*cooperative=*/true, stream),
                "loopback fused launch");
   }

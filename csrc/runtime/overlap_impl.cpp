@@ -439,6 +439,80 @@ void OverlapImpl::GemmReduceScatterFused(at::Tensor A, at::Tensor B, at::Tensor 
             static_cast<int>(Algo));
 }
 
+void OverlapImpl::GemmAll2AllFused(at::Tensor A, at::Tensor B, at::Tensor D, int64_t Algo,
+                                   at::Tensor mLen_CPU) {
+  FO_CHECK(heap_ != nullptr, "call nccl_init first");
+  FO_CHECK(!mLen_CPU.is_cuda() && mLen_CPU.scalar_type() == at::kInt && mLen_CPU.is_contiguous() &&
+               mLen_CPU.numel() == static_cast<int64_t>(world_) * world_,
+           "mLen_CPU must be a contiguous int32 host tensor of shape [world, world]");
+  if (world_ == 1) return;  // a rank's own rows are not part of the exchange
+  c10::cuda::CUDAGuard guard(A.device());
+  const int algo = static_cast<int>(Algo);
+  GemmTensorMaps maps;
+  GemmParams p;
+  std::memset(&p, 0, sizeof(p));
+  bool bf16 = true;
+  setup_problem(algo, A, B, 0, &maps, &p, &bf16);
+
+  const int* ml = mLen_CPU.data_ptr<int>();
+  for (int i = 0; i < world_ * world_; ++i) FO_CHECK(ml[i] >= 0, "mLen_CPU holds a negative row count");
+  const All2AllPlan plan = all2all_plan(ml, world_, rank_);
+  FO_CHECK(plan.send_rows <= p.M, "mLen_CPU sends ", plan.send_rows, " rows but A has only ", p.M);
+  check_out(D, A, plan.recv_rows * p.N, "D");
+
+  // Destination addresses.  Every rank must take the same branch: D comes from symm_empty on
+  // all ranks or on none.
+  const size_t recv_bytes = static_cast<size_t>(plan.recv_rows) * p.N * 2;
+  const SymmetricRegion* reg = heap_->find(D.data_ptr(), std::max<size_t>(recv_bytes, 1));
+  bool copy_back = false;
+  if (reg != nullptr) {
+    const size_t off = static_cast<char*>(D.data_ptr()) - static_cast<char*>(reg->local());
+    for (int r = 0; r < world_; ++r) p.dst[r] = static_cast<char*>(reg->ptr[r]) + off;
+  } else {
+    int64_t max_recv = 0;  // the scratch is one collective allocation: same size everywhere
+    for (int r = 0; r < world_; ++r) max_recv = std::max(max_recv, all2all_plan(ml, world_, r).recv_rows);
+    const size_t bytes = std::max<size_t>(static_cast<size_t>(max_recv) * p.N * 2, 256);
+    if (out_ == nullptr || out_->bytes < bytes) out_ = heap_->allocate(bytes, stream());
+    for (int r = 0; r < world_; ++r) p.dst[r] = out_->ptr[r];
+    copy_back = true;
+  }
+  if (signal_ == nullptr) signal_ = heap_->allocate(kSignalBytes, stream());
+
+  at::Tensor tab = at::zeros({2 * kMaxRanks}, at::TensorOptions().dtype(at::kInt));
+  for (int d = 0; d < kMaxRanks; ++d) {
+    tab.data_ptr<int>()[d] = plan.row_end[d];
+    tab.data_ptr<int>()[kMaxRanks + d] = plan.dst_row[d];
+  }
+  a2a_tab_ = tab.to(at::Device(at::kCUDA, device_));
+
+  ++epoch_;
+  ++a2a_epoch_;
+  set_l2_hints(&p, opt_l2_hints_ != 0);
+  p.out_mode = kOutAll2All;
+  p.rldn = 1;
+  p.comm = kCommFusedA2A;
+  p.ws = world_;
+  p.rank_base = rank_;
+  p.epoch_done = static_cast<uint32_t>(world_) * epoch_;
+  p.epoch_ready = static_cast<uint32_t>(world_) * a2a_epoch_;
+  p.timeout_ns = static_cast<uint64_t>(opt_timeout_ms_) * 1000000ull;
+  p.a2a_tab = a2a_tab_.data_ptr<int>();
+  p.status[0] = status_.data_ptr<int>();
+  p.local_cnt[0] =
+      reinterpret_cast<uint32_t*>(static_cast<char*>(signal_->local()) + kSignalLocalCntOffset);
+  for (int r = 0; r < world_; ++r) {
+    char* sig = static_cast<char*>(signal_->ptr[r]);
+    p.done[r] = reinterpret_cast<uint32_t*>(sig + kSignalDoneOffset);
+    p.ready[r] = reinterpret_cast<uint32_t*>(sig + kSignalReadyOffset);
+  }
+  const int grid = std::max(1, std::min(gemm_max_resident_ctas(algo, bf16, false), p.num_tiles));
+  cuda_check(launch_gemm(algo, bf16, false, maps, p, grid, 1, false, stream()), "all-to-all GEMM launch");
+  if (copy_back && recv_bytes > 0) {
+    cuda_check(cudaMemcpyAsync(D.data_ptr(), out_->local(), recv_bytes, cudaMemcpyDeviceToDevice, stream()),
+               "cudaMemcpyAsync");
+  }
+}
+
 // ---------------------------------------------------------------------------- reference API
 
 namespace {

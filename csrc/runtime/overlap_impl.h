@@ -53,6 +53,13 @@ class OverlapImpl : public torch::CustomClassHolder {
   // Fused collectives with row-major results and one flag per tile: no RA / cSeg needed.
   void GemmAllReduceFused(at::Tensor A, at::Tensor B, at::Tensor C, int64_t Algo);
   void GemmReduceScatterFused(at::Tensor A, at::Tensor B, at::Tensor D, int64_t Algo);
+  // GEMM whose epilogue stores every row of A * B^T straight into the receive buffer D of the
+  // rank it is bound for, over NVLink; same row bookkeeping as gemm_all2all (mLen_CPU[r][i]
+  // rows go from rank r to rank i, runs packed in rank order, own run excluded), no C and no
+  // separate collective.  Rows of the product past the last run are dropped.  D needs room for
+  // the rows this rank receives; a D from symm_empty is written in place, any other D through
+  // a symmetric scratch buffer and one copy.  The reference has no overlapped all-to-all.
+  void GemmAll2AllFused(at::Tensor A, at::Tensor B, at::Tensor D, int64_t Algo, at::Tensor mLen_CPU);
   // Options: "mode" (0 fused, 1 gated), "strided_rows" (reduce-scatter row ownership:
   // 1 = rank r owns rows i % world == r as in the reference, 0 = contiguous blocks),
   // "sm_margin" (SMs left to NCCL in gated mode), "timeout_ms" (bound of device waits),
@@ -115,6 +122,8 @@ class OverlapImpl : public torch::CustomClassHolder {
   SymmetricRegion* out_ = nullptr;  // symmetric AllReduce output when the caller's is not
   const SymmetricRegion* user_stage_ = nullptr;  // staging handed in through UseStage
   uint32_t epoch_ = 0;
+  uint32_t a2a_epoch_ = 0;  // fused all-to-all calls so far (start-of-call handshake)
+  at::Tensor a2a_tab_;      // device copy of the current call's row tables
   at::Tensor status_;  // int32[kStatusWords] on the device
 
   int64_t opt_mode_ = 0;

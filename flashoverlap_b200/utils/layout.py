@@ -225,3 +225,23 @@ def integer_compositions(n: int, max_parts: Optional[int] = None) -> Iterable[Li
             parts.pop()
 
     yield from rec(n, [])
+
+
+def all2all_reference(C_per_rank, mlen):
+    """CPU/torch oracle of the variable-size all-to-all on packed rows (the reference's
+    semantics, src/overlap_impl.cu:181-212): ``C_per_rank[r]`` holds rank r's rows, the runs for
+    the other ranks packed in rank order (``mlen[r][i]`` rows for rank i, own run absent);
+    returns the receive buffers, where rank i finds the runs of the other ranks in rank order."""
+    ws = len(C_per_rank)
+    send_off = [[0] * ws for _ in range(ws)]
+    for r in range(ws):
+        acc = 0
+        for i in range(ws):
+            send_off[r][i] = acc
+            if i != r:
+                acc += int(mlen[r][i])
+    out = []
+    for i in range(ws):
+        parts = [C_per_rank[r][send_off[r][i]:send_off[r][i] + int(mlen[r][i])] for r in range(ws) if r != i]
+        out.append(torch.cat(parts, 0) if parts else C_per_rank[i][:0])
+    return out

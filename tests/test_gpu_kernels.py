@@ -7,6 +7,8 @@ import torch
 from flashoverlap_b200 import ops
 from flashoverlap_b200.utils import config, layout
 
+from tests.conftest import experimental
+
 pytestmark = pytest.mark.gpu
 
 
@@ -201,6 +203,27 @@ def test_fused_loopback_pull_protocol(cuda, comm_op):
     _loopback_case(cuda, comm_op, 8, 1024, 1024, 128, 2, False, True, stage_local=True)
     _loopback_case(cuda, comm_op, 2, 2048, 2048, 256, 0, True, False, repeat=3, groups=[40, 50, 38],
                    dt=torch.float16, stage_local=True)
+
+
+@experimental
+@pytest.mark.parametrize("ws,algo,dt", [(2, 0, torch.bfloat16), (4, 2, torch.bfloat16), (8, 0, torch.float16)])
+def test_gemm_all2all_loopback(cuda, ws, algo, dt):
+    """GEMM whose epilogue stores each row into its destination rank's receive buffer."""
+    M, N, K = 1024, 1024, 256
+    g = torch.Generator().manual_seed(ws)
+    mlen = torch.randint(0, M // (ws - 1) + 1, (ws, ws), generator=g, dtype=torch.int32)
+    mlen[0, 1 % ws] = 0                                           # an empty run
+    A = [_rand((M, K), dt, cuda) for _ in range(ws)]
+    B = [_rand((N, K), dt, cuda) for _ in range(ws)]
+    C = [(a.float() @ b.float().t()) for a, b in zip(A, B)]
+    want = layout.all2all_reference(C, mlen.tolist())
+    out = [torch.full((max(1, w.shape[0]), N), float("nan"), device=cuda, dtype=dt) for w in want]
+    st = ops.fused_loopback("all_to_all", A, B, out, algo=algo, repeat=2, timeout_ms=2000, mlen=mlen)
+    assert all(s[0] == 0 for s in st), st
+    for r in range(ws):
+        n = want[r].shape[0]
+        if n:
+            assert (out[r][:n].float() - want[r]).abs().max().item() <= _tol(want[r]), r
 
 
 def test_fused_loopback_eight_ranks(cuda):

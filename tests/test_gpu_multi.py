@@ -10,6 +10,7 @@ import torch
 import torch.distributed as dist
 
 from tests._mp import run_ranks
+from tests.conftest import experimental
 
 pytestmark = pytest.mark.gpu
 
@@ -110,7 +111,7 @@ def _pull_worker(rank, world):
     dev = torch.device("cuda", rank)
     impl = _setup(rank, world)
     impl.set_option("stage_local", 1)
-    switch_reduce = os.environ.get("FLASHOVERLAP_TEST_SWITCH_REDUCE", "0") == "1"
+    switch_reduce = os.environ.get("FLASHOVERLAP_EXPERIMENTAL", "0") == "1"
     res = {"info_switch_reduce": 0.0}
     for (M, N, K, algo) in ((1024, 2048, 512, 0), (2048, 2048, 512, 1), (2048, 1024, 256, 3)):
         BM = config.algo_params(algo)["BM"]
@@ -143,12 +144,48 @@ def _pull_worker(rank, world):
 
 
 def test_pull_protocol_multi_gpu(lib):
-    """Set FLASHOVERLAP_TEST_SWITCH_REDUCE=1 to also stage in multicast-mapped memory, where the
+    """With FLASHOVERLAP_EXPERIMENTAL=1 the staging also goes to multicast-mapped memory, where the
     owners' reducers sum with multimem.ld_reduce."""
     world = _world()
     for r in run_ranks(_pull_worker, world, "nccl"):
         assert r.pop("status") == 0
         print("switch-side reduction used:", bool(r.pop("info_switch_reduce")))
+        for k, v in r.items():
+            assert v <= 1.0, (k, v)
+
+
+def _all2all_worker(rank, world):
+    from flashoverlap_b200.utils import layout
+    dev = torch.device("cuda", rank)
+    impl = _setup(rank, world)
+    res = {}
+    M, N, K = 2048, 1024, 256
+    g = torch.Generator().manual_seed(99)                          # same matrix on every rank
+    mlen = torch.randint(0, M // (world - 1) + 1, (world, world), generator=g, dtype=torch.int32)
+    for algo in (0, 1, 3):
+        A, B = _rand((M, K), dev, 50 + rank), _rand((N, K), dev, 60 + rank)
+        C = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+        recv = int(mlen[:, rank].sum() - mlen[rank, rank])
+        Dref = torch.full((max(recv, 1), N), float("nan"), device=dev, dtype=torch.bfloat16)
+        impl.gemm_all2all(A, B, C, Dref, algo, mlen)              # GEMM, then grouped NCCL send/recv
+        for symmetric in (True, False):
+            D = impl.symm_empty([max(recv, 1), N], "bfloat16") if symmetric else torch.empty_like(Dref)
+            for _ in range(3):
+                D.fill_(float("nan"))
+                impl.gemm_all2all_fused(A, B, D, algo, mlen)
+            torch.cuda.synchronize(); dist.barrier()
+            tol = 0.02 * Dref[:recv].float().abs().max().item() + 1e-3 if recv else 1.0
+            err = (D[:recv].float() - Dref[:recv].float()).abs().max().item() if recv else 0.0
+            res[f"a2a_{algo}_{int(symmetric)}"] = err / tol
+    res["status"] = impl.read_status()[0]
+    return res
+
+
+@experimental
+def test_gemm_all2all_fused_multi_gpu(lib):
+    world = _world()
+    for r in run_ranks(_all2all_worker, world, "nccl"):
+        assert r.pop("status") == 0
         for k, v in r.items():
             assert v <= 1.0, (k, v)
 
