@@ -8,6 +8,7 @@
 #include <cstring>
 
 #include "../comm/nccl_utils.h"
+#include "../common/fo_nvtx.h"
 #include "../flags/fo_wait.h"
 #include "fused_common.h"
 
@@ -227,6 +228,7 @@ void OverlapImpl::run_plain(const at::Tensor& A, const at::Tensor& B, void* out,
 }
 
 void OverlapImpl::Gemm(at::Tensor A, at::Tensor B, at::Tensor C, int64_t Algo) {
+  NvtxRange nvtx_range("flashoverlap::cutlass_gemm");
   const GemmShape s = check_operands(A, B);
   check_out(C, A, static_cast<int64_t>(s.M) * s.N, "C");
   run_plain(A, B, C.data_ptr(), kOutNatural, nullptr, nullptr, 1, nullptr, 0, false, false, nullptr,
@@ -236,12 +238,14 @@ void OverlapImpl::Gemm(at::Tensor A, at::Tensor B, at::Tensor C, int64_t Algo) {
 // ---------------------------------------------------------------------------- bare collectives
 
 void OverlapImpl::NcclAllReduce(at::Tensor C) {
+  NvtxRange nvtx_range("flashoverlap::nccl_allreduce");
   if (world_ == 1) return;
   FO_NCCL_CHECK(ncclAllReduce(C.data_ptr(), C.data_ptr(), C.numel(), nccl_dtype(C), ncclSum, comm_,
                               stream()));
 }
 
 void OverlapImpl::SegAllReduce(at::Tensor C, at::Tensor cSEG_CPU, int64_t SegNum) {
+  NvtxRange nvtx_range("flashoverlap::seg_allreduce");
   // Equal units of numel / SegNum elements; segment s covers cSEG_CPU[s] units
   // (reference: src/overlap_impl.cu:153-168).
   if (world_ == 1) return;
@@ -262,6 +266,7 @@ void OverlapImpl::SegAllReduce(at::Tensor C, at::Tensor cSEG_CPU, int64_t SegNum
 }
 
 void OverlapImpl::NcclReduceScatter(at::Tensor C) {
+  NvtxRange nvtx_range("flashoverlap::nccl_reducescatter");
   // In place: rank r's shard of the sum lands in its own slice of C
   // (reference: src/overlap_impl.cu:170-179).
   if (world_ == 1) return;
@@ -272,6 +277,7 @@ void OverlapImpl::NcclReduceScatter(at::Tensor C) {
 }
 
 void OverlapImpl::NcclAll2All(at::Tensor C, at::Tensor D, at::Tensor mLen_CPU) {
+  NvtxRange nvtx_range("flashoverlap::nccl_all2all");
   // Variable-size all-to-all on packed rows: rank r sends mLen[r][i] rows to rank i and
   // receives mLen[i][r] rows from it; a rank's own rows are not part of C or D
   // (reference: src/overlap_impl.cu:181-212).
@@ -301,12 +307,14 @@ void OverlapImpl::NcclAll2All(at::Tensor C, at::Tensor D, at::Tensor mLen_CPU) {
 // ---------------------------------------------------------------------------- non-overlapped
 
 void OverlapImpl::GemmAllReduce(at::Tensor A, at::Tensor B, at::Tensor C, int64_t Algo) {
+  NvtxRange nvtx_range("flashoverlap::gemm_allreduce");
   Gemm(A, B, C, Algo);
   NcclAllReduce(C);
 }
 
 void OverlapImpl::GemmReduceScatter(at::Tensor A, at::Tensor B, at::Tensor C, at::Tensor D,
                                     int64_t Algo) {
+  NvtxRange nvtx_range("flashoverlap::gemm_reducescatter");
   Gemm(A, B, C, Algo);
   const int64_t recv = C.numel() / world_;
   check_out(D, A, recv, "D");
@@ -322,6 +330,7 @@ void OverlapImpl::GemmReduceScatter(at::Tensor A, at::Tensor B, at::Tensor C, at
 
 void OverlapImpl::GemmAll2All(at::Tensor A, at::Tensor B, at::Tensor C, at::Tensor D, int64_t Algo,
                               at::Tensor mLen_CPU) {
+  NvtxRange nvtx_range("flashoverlap::gemm_all2all");
   Gemm(A, B, C, Algo);
   NcclAll2All(C, D, mLen_CPU);
 }
@@ -422,6 +431,7 @@ void OverlapImpl::run_fused(int comm, const at::Tensor& A, const at::Tensor& B, 
 }
 
 void OverlapImpl::GemmAllReduceFused(at::Tensor A, at::Tensor B, at::Tensor C, int64_t Algo) {
+  NvtxRange nvtx_range("flashoverlap::gemm_allreduce_fused");
   if (world_ == 1) {
     Gemm(A, B, C, Algo);
     return;
@@ -431,6 +441,7 @@ void OverlapImpl::GemmAllReduceFused(at::Tensor A, at::Tensor B, at::Tensor C, i
 }
 
 void OverlapImpl::GemmReduceScatterFused(at::Tensor A, at::Tensor B, at::Tensor D, int64_t Algo) {
+  NvtxRange nvtx_range("flashoverlap::gemm_reducescatter_fused");
   if (world_ == 1) {
     Gemm(A, B, D, Algo);
     return;
@@ -441,6 +452,7 @@ void OverlapImpl::GemmReduceScatterFused(at::Tensor A, at::Tensor B, at::Tensor 
 
 void OverlapImpl::GemmAll2AllFused(at::Tensor A, at::Tensor B, at::Tensor D, int64_t Algo,
                                    at::Tensor mLen_CPU) {
+  NvtxRange nvtx_range("flashoverlap::gemm_all2all_fused");
   FO_CHECK(heap_ != nullptr, "call nccl_init first");
   FO_CHECK(!mLen_CPU.is_cuda() && mLen_CPU.scalar_type() == at::kInt && mLen_CPU.is_contiguous() &&
                mLen_CPU.numel() == static_cast<int64_t>(world_) * world_,
@@ -526,6 +538,7 @@ int* mm_ptr(const at::Tensor& MM) {
 void OverlapImpl::GemmAllReduceOverlap(at::Tensor A, at::Tensor B, at::Tensor C, at::Tensor MM,
                                        at::Tensor RA, int64_t rLDN, at::Tensor cSEG_CPU,
                                        at::Tensor cSEG_GPU, int64_t Algo, bool if_monitor) {
+  NvtxRange nvtx_range("flashoverlap::gemm_allreduce_overlap");
   const GemmShape s = check_operands(A, B);
   check_out(C, A, static_cast<int64_t>(s.M) * s.N, "C");
   const AlgoConfig c = algo_config(static_cast<int>(Algo));
@@ -554,6 +567,7 @@ void OverlapImpl::GemmReduceScatterOverlap(at::Tensor A, at::Tensor B, at::Tenso
                                            at::Tensor MM, at::Tensor RA, at::Tensor RE,
                                            int64_t rLDN, at::Tensor cSEG_CPU, at::Tensor cSEG_GPU,
                                            int64_t Algo, bool if_monitor) {
+  NvtxRange nvtx_range("flashoverlap::gemm_reducescatter_overlap");
   const GemmShape s = check_operands(A, B);
   check_out(D, A, static_cast<int64_t>(s.M) * s.N / world_, "D");
   const AlgoConfig c = algo_config(static_cast<int>(Algo));
