@@ -63,6 +63,16 @@ def worker(rank, world, args):
     res["nonoverlap_ms"] = perf_ms(wl.run_nonoverlap, WARM_UP, args.reps, f)
     wl.set_cseg([1] * wl.tiles if "cSeg" not in cfg or cfg.get("mode") == "gated" else cfg["cSeg"])
     res["fused_ms"] = perf_ms(wl.run, WARM_UP, args.reps, f)
+    if world > 1 and args.pull:
+        # pull protocol: partials stay on the producing GPU; owners fetch them with peer loads,
+        # then (staging with a multicast mapping) with one switch-side reduction per vector
+        from flashoverlap_b200.parallel import symm
+        impl.set_option("stage_local", 1)
+        res["fused_pull_peer_ms"] = perf_ms(wl.run, WARM_UP, args.reps, f)
+        _, switch = symm.alloc_stage(impl, args.m, args.n, dt)
+        if switch:
+            res["fused_pull_switch_ms"] = perf_ms(wl.run, WARM_UP, args.reps, f)
+        impl.set_option("stage_local", 0)
     if world > 1:
         wl.mode = "gated"
         wave = sm - margin
@@ -94,6 +104,9 @@ def worker(rank, world, args):
             print(f"{'overlap (gated NCCL)':>24} {res['gated_ms']:.4f} ms   speedup {res['speedup_gated']:.3f}")
         print(f"{'overlap (fused)':>24} {res['fused_ms']:.4f} ms   speedup {res['speedup_fused']:.3f}   "
               f"roofline {res['roofline_ms']:.4f} ms ({100 * res['roofline_frac']:.1f}% of measured peaks)")
+        for key, label in (("fused_pull_peer_ms", "fused, pull (peer loads)"), ("fused_pull_switch_ms", "fused, pull (switch sum)")):
+            if key in res:
+                print(f"{label:>24} {res[key]:.4f} ms   speedup {res['baseline_ms'] / res[key]:.3f}")
         print(json.dumps({k: (round(v, 5) if isinstance(v, float) else v) for k, v in res.items()}))
     return res
 
@@ -109,6 +122,9 @@ def main():
     ap.add_argument("--path", default=None)
     ap.add_argument("--reps", type=int, default=REP)
     ap.add_argument("--flush", action="store_true", help="flush L2 between timed iterations")
+    ap.add_argument("--pull", action="store_true",
+                    help="also time the pull protocol of the fused kernel (option stage_local), with peer loads "
+                         "and with the NVSwitch reduction")
     args = ap.parse_args()
     run_on_all_gpus(worker, args)
 
