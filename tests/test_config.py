@@ -45,3 +45,27 @@ def test_default_solution_is_consistent():
     assert (c["Algo"] & 3) == 1 and sorted(c["hint"]) == list(range((768 // 128) * (2048 // 256)))
     c = config.default_solution(1024, 2048, algo=7)            # two halves per CTA: units of 4 tile rows
     assert (c["Algo"] & 3) == 3 and c["hint"][:4] == [0, 8, 16, 24]
+
+
+def test_gen_config_csv_rows_map_back_to_algos(tmp_path, monkeypatch):
+    """tune/gen_config.py: a CSV row that names a kernel of the table yields its Algo index."""
+    import csv
+    import importlib
+    import os
+    import sys
+
+    tune_dir = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "tune")
+    monkeypatch.syspath_prepend(tune_dir)
+    gen_config = importlib.import_module("gen_config")
+    algos = [0, 1, 2, 3, 7, 13, 19, 22]
+    path = tmp_path / "cands.csv"
+    with open(path, "w", newline="") as f:
+        w = csv.DictWriter(f, fieldnames=["cta_m", "cta_n", "cta_k", "stages", "raster", "cta_group", "runtime"])
+        w.writeheader()
+        for i, a in enumerate(algos):
+            p = config.algo_params(a)
+            w.writerow({"cta_m": p["BM"] * p["mt"], "cta_n": p["BN"], "cta_k": p["BK"], "stages": p["stages"],
+                        "raster": p["raster"], "cta_group": 1 + p["cta2"], "runtime": 1.0 + i})
+        w.writerow({"cta_m": 64, "cta_n": 64, "cta_k": 32, "stages": 3, "raster": 1, "cta_group": 1, "runtime": 0.5})
+    assert gen_config.candidates_from_csv(str(path)) == algos      # the unknown row is skipped
+    sys.modules.pop("gen_config", None)
