@@ -67,6 +67,12 @@ def is_current() -> bool:
     return lib_path().exists() and stamp.exists() and stamp.read_text().strip() == source_hash()
 
 
+def write_stamp() -> None:
+    """Records the current source hash beside the library (the CMake build calls this)."""
+    _LIB_DIR.mkdir(parents=True, exist_ok=True)
+    (_LIB_DIR / (_LIB_NAME + ".hash")).write_text(source_hash() + "\n")
+
+
 def _nccl_paths() -> tuple[str, str]:
     site = Path(sysconfig.get_paths()["purelib"])
     inc = site / "nvidia" / "nccl" / "include"
@@ -100,7 +106,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     built = build_dir / (_EXT_NAME + ".so")
     _LIB_DIR.mkdir(parents=True, exist_ok=True)
     shutil.copy2(built, lib_path())
-    (_LIB_DIR / (_LIB_NAME + ".hash")).write_text(source_hash() + "\n")
+    write_stamp()
     global _loaded
     _loaded = True  # cpp_extension.load already registered the ops in this process
     return lib_path()
