@@ -187,6 +187,7 @@ TORCH_LIBRARY(flashoverlap_class, m) {
       .def("gemm_allreduce_fused", &OverlapImpl::GemmAllReduceFused)
       .def("gemm_reducescatter_fused", &OverlapImpl::GemmReduceScatterFused)
       .def("gemm_all2all_fused", &OverlapImpl::GemmAll2AllFused)
+      .def("gemm_reducescatter_rmsnorm_fused", &OverlapImpl::GemmReduceScatterRmsNormFused)
       .def("set_option", &OverlapImpl::SetOption)
       .def("get_option", &OverlapImpl::GetOption)
       .def("symm_empty", &OverlapImpl::SymmEmpty)

@@ -90,6 +90,13 @@ struct GemmParams {
   // receive buffers may be overwritten from then on); nobody stores before it reaches epoch_ready.
   uint32_t* ready[kMaxRanks];
   uint32_t epoch_ready;
+  // ReduceScatter with the RMSNorm tail fused into the reducers (row-major shard only): weight
+  // [N] in the operands' type, per-row sums of squares [virtual rank][M / ws] (fp32, zero between
+  // calls), per-row-panel counters of reduced tiles [virtual rank][tiles_m] (zero between calls).
+  float norm_eps;
+  const void* norm_w;
+  float* row_ssq;
+  int* panel_cnt;
 };
 
 // ------------------------------------------------------------------ Algo table

@@ -202,6 +202,137 @@ __device__ __forceinline__ void reduce_tile(const GemmParams& p, int me, int rt,
   }
 }
 
+// ReduceScatter reduction that also gathers the RMSNorm statistics: sums the WS partials of the
+// owned rows of one tile, writes the rounded sums to the row-major local shard and adds each
+// row's sum of squares (of the rounded values, as a separate norm kernel would see them) to
+// row_ssq.  One row of a tile is BN / 8 vectors = a whole warp (BN = 256) or half of one.
+template <int BN, bool BF16, int WS>
+__device__ __forceinline__ void reduce_tile_ssq(const GemmParams& p, int me, int rt, const uint8_t* src_tile,
+                                                size_t src_stride_bytes, size_t out_base, float* row_ssq) {
+  constexpr int kVecPerRow = BN / 8;
+  constexpr int kRowsOwned = kBM / WS;
+  constexpr int kTotalVec = kRowsOwned * kVecPerRow;
+  constexpr int U = (16 / WS) < 1 ? 1 : (16 / WS);
+  static_assert(kTotalVec % (kReducerThreads * U) == 0, "tile slice must split evenly over the reducer threads");
+  static_assert(kVecPerRow == 32 || kVecPerRow == 16, "a row must be a warp or half a warp of vectors");
+  const int lane = rt & 31;
+  for (int v0 = rt; v0 < kTotalVec; v0 += kReducerThreads * U) {
+    uint4 x[U][WS];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int v = v0 + u * kReducerThreads;
+      const int q = v / kVecPerRow;
+      const int c8 = v - q * kVecPerRow;
+      const uint8_t* sp = src_tile + (static_cast<size_t>(q) * BN + c8 * 8) * 2;
+#pragma unroll
+      for (int s = 0; s < WS; ++s) x[u][s] = ptx::ld_cg_v4(sp + static_cast<size_t>(s) * src_stride_bytes);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int v = v0 + u * kReducerThreads;
+      const int q = v / kVecPerRow;
+      const int c8 = v - q * kVecPerRow;
+      float a[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) a[i] = 0.f;
+#pragma unroll
+      for (int s = 0; s < WS; ++s) {
+        unpack_add<BF16>(x[u][s].x, a[0], a[1]);
+        unpack_add<BF16>(x[u][s].y, a[2], a[3]);
+        unpack_add<BF16>(x[u][s].z, a[4], a[5]);
+        unpack_add<BF16>(x[u][s].w, a[6], a[7]);
+      }
+      uint4 y;
+      y.x = pack2<BF16>(a[0], a[1]);
+      y.y = pack2<BF16>(a[2], a[3]);
+      y.z = pack2<BF16>(a[4], a[5]);
+      y.w = pack2<BF16>(a[6], a[7]);
+      const size_t off = (out_base + static_cast<size_t>(q) * p.N + c8 * 8) * 2;
+      ptx::st_v4(reinterpret_cast<uint8_t*>(p.dst[me]) + off, y);
+      // sum of squares of the rounded values
+      float r[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) r[i] = 0.f;
+      unpack_add<BF16>(y.x, r[0], r[1]);
+      unpack_add<BF16>(y.y, r[2], r[3]);
+      unpack_add<BF16>(y.z, r[4], r[5]);
+      unpack_add<BF16>(y.w, r[6], r[7]);
+      float ss = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) ss += r[i] * r[i];
+#pragma unroll
+      for (int o = kVecPerRow / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      if ((lane & (kVecPerRow - 1)) == 0) atomicAdd(row_ssq + q, ss);
+    }
+  }
+}
+
+// y = round16(round16(x * scale) * w), the arithmetic of the stand-alone RMSNorm kernels.
+template <bool BF16>
+__device__ __forceinline__ uint32_t norm_scale_mul2(uint32_t x, uint32_t w, float scale) {
+  float lo = 0.f, hi = 0.f;
+  unpack_add<BF16>(x, lo, hi);
+  if constexpr (BF16) {
+    __nv_bfloat162 n = __floats2bfloat162_rn(lo * scale, hi * scale);
+    __nv_bfloat162 r = __hmul2(n, *reinterpret_cast<__nv_bfloat162*>(&w));
+    return *reinterpret_cast<uint32_t*>(&r);
+  } else {
+    __half2 n = __floats2half2_rn(lo * scale, hi * scale);
+    __half2 r = __hmul2(n, *reinterpret_cast<__half2*>(&w));
+    return *reinterpret_cast<uint32_t*>(&r);
+  }
+}
+
+// RMSNorm of the `rows` shard rows starting at `row0` (all their tiles have been reduced and
+// their sums of squares are complete): normalises in place.  A thread keeps kJV weight vectors
+// in registers and walks down the rows two at a time, so 2 * kJV loads are in flight per
+// thread; the rows were written moments ago and come from L2.
+template <bool BF16>
+__device__ __forceinline__ void normalise_panel(const GemmParams& p, int me, int rt, int row0, int rows,
+                                                const float* row_ssq) {
+  constexpr int kJV = 4;
+  const int nvec = p.N / 8;
+  uint8_t* base = reinterpret_cast<uint8_t*>(p.dst[me]) + static_cast<size_t>(row0) * p.N * 2;
+  const uint8_t* w = reinterpret_cast<const uint8_t*>(p.norm_w);
+  const size_t pitch = static_cast<size_t>(p.N) * 2;
+  const float inv_n = 1.f / static_cast<float>(p.N);
+  for (int j0 = rt; j0 < nvec; j0 += kReducerThreads * kJV) {
+    uint4 wv[kJV];
+#pragma unroll
+    for (int i = 0; i < kJV; ++i) {
+      const int j = j0 + i * kReducerThreads;
+      if (j < nvec) wv[i] = __ldg(reinterpret_cast<const uint4*>(w + static_cast<size_t>(j) * 16));
+    }
+    for (int q = 0; q < rows; q += 2) {  // rows is 128 / ws: even
+      uint4 x[2][kJV];
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+#pragma unroll
+        for (int i = 0; i < kJV; ++i) {
+          const int j = j0 + i * kReducerThreads;
+          if (j < nvec) x[r][i] = ptx::ld_cg_v4(base + (q + r) * pitch + static_cast<size_t>(j) * 16);
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        const float scale = rsqrtf(__ldcg(row_ssq + q + r) * inv_n + p.norm_eps);
+#pragma unroll
+        for (int i = 0; i < kJV; ++i) {
+          const int j = j0 + i * kReducerThreads;
+          if (j < nvec) {
+            uint4 y;
+            y.x = norm_scale_mul2<BF16>(x[r][i].x, wv[i].x, scale);
+            y.y = norm_scale_mul2<BF16>(x[r][i].y, wv[i].y, scale);
+            y.z = norm_scale_mul2<BF16>(x[r][i].z, wv[i].z, scale);
+            y.w = norm_scale_mul2<BF16>(x[r][i].w, wv[i].w, scale);
+            ptx::st_v4(base + (q + r) * pitch + static_cast<size_t>(j) * 16, y);
+          }
+        }
+      }
+    }
+  }
+}
+
 // Pull variant of the reduction: the partials of the rows this rank owns sit at the same offset
 // `tile_off` (bytes) of EVERY rank's staging buffer.  With a multicast mapping of the staging one
 // multimem.ld_reduce per vector lets the NVSwitch fetch and sum all ranks' copies (fp32
@@ -290,10 +421,11 @@ __device__ __forceinline__ void reduce_tile_pull(const GemmParams& p, int me, in
   }
 }
 
-template <int BN, int STAGES, bool BF16, bool FUSED, bool CTA2, int MT, bool A2A = false>
+template <int BN, int STAGES, bool BF16, bool FUSED, bool CTA2, int MT, bool A2A = false, bool NORM = false>
 __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
     fo_gemm_kernel(const __grid_constant__ GemmTensorMaps maps,
                    const __grid_constant__ GemmParams p) {
+  static_assert(!NORM || FUSED, "the RMSNorm tail belongs to the fused reduce-scatter");
   static_assert(MT == 1 || (MT == 2 && CTA2 && BN == 256), "two row halves need CTA pairs and BN = 256");
   static_assert(!(A2A && FUSED), "the all-to-all epilogue is a variant of the plain kernel");
   using L = GemmSmem<BN, STAGES, CTA2, MT>;
@@ -796,6 +928,34 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
 
         const size_t stride_b = src_stride * 2;
         if (p.diag & 1) continue;
+        if constexpr (NORM) {
+          // ReduceScatter + RMSNorm: reduce into the row-major shard while gathering each row's
+          // sum of squares; whoever reduces the last tile of a row panel normalises the panel,
+          // whose rows were written moments ago and are still in L2.
+          float* ssq = p.row_ssq + static_cast<size_t>(vr) * (p.M / ws) + static_cast<size_t>(tc.m) * rows_owned;
+          int* cnt = p.panel_cnt + vr * p.tiles_m + tc.m;
+          switch (ws) {
+            case 2: reduce_tile_ssq<BN, BF16, 2>(p, me, rt, src_tile, stride_b, out_base, ssq); break;
+            case 4: reduce_tile_ssq<BN, BF16, 4>(p, me, rt, src_tile, stride_b, out_base, ssq); break;
+            default: reduce_tile_ssq<BN, BF16, 8>(p, me, rt, src_tile, stride_b, out_base, ssq); break;
+          }
+          ptx::named_bar_sync(2, kReducerThreads);  // every thread's stores and atomics are issued
+          if (rt == 0) {
+            __threadfence();
+            const int old = atomicAdd(cnt, 1);
+            *s_is_last = (old == p.tiles_n - 1) ? 1 : 0;
+            if (old == p.tiles_n - 1) __threadfence();
+          }
+          ptx::named_bar_sync(2, kReducerThreads);
+          if (*s_is_last) {
+            normalise_panel<BF16>(p, me, rt, tc.m * rows_owned, rows_owned, ssq);
+            ptx::named_bar_sync(2, kReducerThreads);
+            if (rt < rows_owned) ssq[rt] = 0.f;
+            if (rt == 0) *cnt = 0;
+          }
+          ptx::named_bar_sync(2, kReducerThreads);  // s_is_last is reused by the next tile
+          continue;
+        }
         if (p.stage_local) {
           // rows of owner `me` inside tile t's [owner][rows owned][BN] block of any rank's staging
           const size_t tile_off = (static_cast<size_t>(t) * kBM + static_cast<size_t>(me) * rows_owned) * BN * 2;

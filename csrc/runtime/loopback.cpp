@@ -15,7 +15,8 @@ std::vector<int64_t> fused_loopback(std::string comm_op, std::vector<at::Tensor>
                                     c10::optional<at::Tensor> cseg_opt, int64_t algo,
                                     bool strided_rows, bool natural_out, int64_t repeat,
                                     int64_t timeout_ms, bool stage_local,
-                                    c10::optional<at::Tensor> mlen_opt) {
+                                    c10::optional<at::Tensor> mlen_opt,
+                                    c10::optional<at::Tensor> norm_w, double norm_eps) {
   const at::Tensor RA = RA_opt.has_value() ? *RA_opt : at::Tensor();
   const at::Tensor cseg_gpu = cseg_opt.has_value() ? *cseg_opt : at::Tensor();
   const int ws = static_cast<int>(A.size());
@@ -98,6 +99,21 @@ std::vector<int64_t> fused_loopback(std::string comm_op, std::vector<at::Tensor>
   if (a2a) {
     p.out_mode = kOutAll2All;
     p.a2a_tab = tab.data_ptr<int>();
+  }
+  at::Tensor row_ssq, panel_cnt;  // RMSNorm tail: statistics of every virtual rank
+  if (norm_w.has_value()) {
+    FO_CHECK(comm == kCommFusedRS && natural_out && !stage_local,
+             "the RMSNorm tail needs a row-major reduce-scatter with the push protocol");
+    FO_CHECK(norm_w->is_cuda() && norm_w->is_contiguous() && norm_w->scalar_type() == A[0].scalar_type() &&
+                 norm_w->numel() == p.N,
+             "norm_w must be a contiguous CUDA tensor of N elements in the operands' dtype");
+    row_ssq = at::zeros({static_cast<int64_t>(p.M)}, at::TensorOptions().dtype(at::kFloat).device(at::kCUDA, dev));
+    panel_cnt = at::zeros({static_cast<int64_t>(ws) * p.tiles_m},
+                          at::TensorOptions().dtype(at::kInt).device(at::kCUDA, dev));
+    p.norm_w = norm_w->data_ptr();
+    p.norm_eps = static_cast<float>(norm_eps);
+    p.row_ssq = row_ssq.data_ptr<float>();
+    p.panel_cnt = panel_cnt.data_ptr<int>();
   }
   if (const char* d = std::getenv("FLASHOVERLAP_DIAG")) p.diag = std::atoi(d);  // timing studies only
   p.timeout_ns = static_cast<uint64_t>(timeout_ms) * 1000000ull;

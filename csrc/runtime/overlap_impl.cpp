@@ -10,6 +10,7 @@
 #include "../comm/nccl_utils.h"
 #include "../common/fo_nvtx.h"
 #include "../flags/fo_wait.h"
+#include "../norm/fo_norm.h"
 #include "fused_common.h"
 
 namespace fo {
@@ -337,11 +338,11 @@ void OverlapImpl::GemmAll2All(at::Tensor A, at::Tensor B, at::Tensor C, at::Tens
 
 // ---------------------------------------------------------------------------- fused path
 
-void OverlapImpl::ensure_fused_buffers(size_t stage_bytes, size_t nflags) {
+void OverlapImpl::ensure_fused_buffers(size_t stage_bytes, size_t nflags, bool pull) {
   FO_CHECK(heap_ != nullptr, "call nccl_init first");
   FO_CHECK(nflags <= kSignalMaxFlags, "too many tiles/groups for the flag region: ", nflags);
   if (signal_ == nullptr) signal_ = heap_->allocate(kSignalBytes, stream());
-  const bool user_stage = opt_stage_local_ != 0 && user_stage_ != nullptr && user_stage_->bytes >= stage_bytes;
+  const bool user_stage = pull && user_stage_ != nullptr && user_stage_->bytes >= stage_bytes;
   if (!user_stage && (stage_ == nullptr || stage_->bytes < stage_bytes)) {
     // A larger shape than any seen so far: take a new region (the old one stays mapped until
     // this object dies, peers may still hold its address).
@@ -351,7 +352,8 @@ void OverlapImpl::ensure_fused_buffers(size_t stage_bytes, size_t nflags) {
 
 void OverlapImpl::run_fused(int comm, const at::Tensor& A, const at::Tensor& B, at::Tensor out,
                             int out_mode, const int* RA, int rldn, int* MM, int mm_stride,
-                            bool monitor, const int* cseg, int num_groups, int algo) {
+                            bool monitor, const int* cseg, int num_groups, int algo,
+                            const at::Tensor* norm_w, double norm_eps) {
   FO_CHECK(heap_ != nullptr, "call nccl_init first");
   c10::cuda::CUDAGuard guard(A.device());
   FO_CHECK(kBM % world_ == 0, "world size must divide the tile height 128");
@@ -364,7 +366,11 @@ void OverlapImpl::run_fused(int comm, const at::Tensor& A, const at::Tensor& B, 
 
   const size_t full_bytes = static_cast<size_t>(p.M) * p.N * 2;
   const size_t nflags = (num_groups > 0 && cseg != nullptr) ? num_groups : p.num_tiles;
-  ensure_fused_buffers(full_bytes, nflags);
+  // Pull protocol: partials stay in the producing rank's staging; a staging buffer with a
+  // multicast mapping (use_stage) lets the switch do the summation.  (The RMSNorm tail is
+  // written for the push protocol.)
+  const bool pull = opt_stage_local_ != 0 && norm_w == nullptr;
+  ensure_fused_buffers(full_bytes, nflags, pull);
 
   const size_t out_bytes = comm == kCommFusedAR ? full_bytes : full_bytes / world_;
   check_out(out, A, static_cast<int64_t>(out_bytes / 2), comm == kCommFusedAR ? "C" : "D");
@@ -407,9 +413,21 @@ void OverlapImpl::run_fused(int comm, const at::Tensor& A, const at::Tensor& B, 
   p.status[0] = status_.data_ptr<int>();
   p.local_cnt[0] =
       reinterpret_cast<uint32_t*>(static_cast<char*>(signal_->local()) + kSignalLocalCntOffset);
-  // Pull protocol: partials stay in the producing rank's staging; a staging buffer with a
-  // multicast mapping (use_stage) lets the switch do the summation.
-  const bool pull = opt_stage_local_ != 0;
+  if (norm_w != nullptr) {
+    FO_CHECK(comm == kCommFusedRS && out_mode == kOutNatural, "the RMSNorm tail needs a row-major reduce-scatter");
+    FO_CHECK(norm_w->is_cuda() && norm_w->is_contiguous() && norm_w->scalar_type() == A.scalar_type() &&
+                 norm_w->numel() == p.N,
+             "W must be a contiguous CUDA tensor of N elements in the operands' dtype");
+    const int64_t rows = p.M / world_;
+    const auto f32 = at::TensorOptions().dtype(at::kFloat).device(at::kCUDA, device_);
+    const auto i32 = at::TensorOptions().dtype(at::kInt).device(at::kCUDA, device_);
+    if (!norm_ssq_.defined() || norm_ssq_.numel() < rows) norm_ssq_ = at::zeros({rows}, f32);
+    if (!norm_cnt_.defined() || norm_cnt_.numel() < p.tiles_m) norm_cnt_ = at::zeros({p.tiles_m}, i32);
+    p.norm_w = norm_w->data_ptr();
+    p.norm_eps = static_cast<float>(norm_eps);
+    p.row_ssq = norm_ssq_.data_ptr<float>();
+    p.panel_cnt = norm_cnt_.data_ptr<int>();
+  }
   const SymmetricRegion* stage =
       (pull && user_stage_ != nullptr && user_stage_->bytes >= full_bytes) ? user_stage_ : stage_;
   p.stage_local = pull ? 1 : 0;
@@ -448,6 +466,27 @@ void OverlapImpl::GemmReduceScatterFused(at::Tensor A, at::Tensor B, at::Tensor 
   }
   run_fused(kCommFusedRS, A, B, D, kOutNatural, nullptr, 1, nullptr, 0, false, nullptr, 0,
             static_cast<int>(Algo));
+}
+
+void OverlapImpl::GemmReduceScatterRmsNormFused(at::Tensor A, at::Tensor B, at::Tensor Y, at::Tensor W,
+                                                double eps, int64_t Algo) {
+  NvtxRange nvtx_range("flashoverlap::gemm_reducescatter_rmsnorm_fused");
+  FO_CHECK(heap_ != nullptr, "call nccl_init first");
+  if (world_ == 1) {
+    // One rank: nothing to reduce; GEMM, then the stand-alone RMSNorm.
+    const GemmShape s = check_operands(A, B);
+    FO_CHECK(W.is_cuda() && W.is_contiguous() && W.scalar_type() == A.scalar_type() && W.numel() == s.N,
+             "W must be a contiguous CUDA tensor of N elements in the operands' dtype");
+    check_out(Y, A, static_cast<int64_t>(s.M) * s.N, "Y");
+    at::Tensor tmp = at::empty({s.M, s.N}, A.options());
+    Gemm(A, B, tmp, Algo);
+    cuda_check(rmsnorm_launch(tmp.data_ptr(), Y.data_ptr(), W.data_ptr(), s.M, s.N, static_cast<float>(eps), s.bf16,
+                              sm_count_, stream()),
+               "rmsnorm");
+    return;
+  }
+  run_fused(kCommFusedRS, A, B, Y, kOutNatural, nullptr, 1, nullptr, 0, false, nullptr, 0,
+            static_cast<int>(Algo), &W, eps);
 }
 
 void OverlapImpl::GemmAll2AllFused(at::Tensor A, at::Tensor B, at::Tensor D, int64_t Algo,

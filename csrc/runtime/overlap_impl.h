@@ -53,6 +53,13 @@ class OverlapImpl : public torch::CustomClassHolder {
   // Fused collectives with row-major results and one flag per tile: no RA / cSeg needed.
   void GemmAllReduceFused(at::Tensor A, at::Tensor B, at::Tensor C, int64_t Algo);
   void GemmReduceScatterFused(at::Tensor A, at::Tensor B, at::Tensor D, int64_t Algo);
+  // Fused GEMM + ReduceScatter + RMSNorm: Y [M/world, N] row-major receives
+  // rmsnorm(reduce_scatter(A * B^T)) * W.  The reducers gather each row's sum of squares while
+  // they reduce, and whichever CTA reduces the last tile of a 128-row panel normalises the
+  // panel's rows in place while they are still in L2 - no separate norm kernel, no second pass
+  // over HBM.  Same arithmetic as reduce-scatter followed by `flashoverlap_op.rmsnorm`.
+  void GemmReduceScatterRmsNormFused(at::Tensor A, at::Tensor B, at::Tensor Y, at::Tensor W, double eps,
+                                     int64_t Algo);
   // GEMM whose epilogue stores every row of A * B^T straight into the receive buffer D of the
   // rank it is bound for, over NVLink; same row bookkeeping as gemm_all2all (mLen_CPU[r][i]
   // rows go from rank r to rank i, runs packed in rank order, own run excluded), no C and no
@@ -96,11 +103,11 @@ class OverlapImpl : public torch::CustomClassHolder {
                  bool monitor, const int* cseg, int num_groups, int algo, int grid_cap);
   void run_fused(int comm, const at::Tensor& A, const at::Tensor& B, at::Tensor out, int out_mode,
                  const int* RA, int rldn, int* MM, int mm_stride, bool monitor, const int* cseg,
-                 int num_groups, int algo);
+                 int num_groups, int algo, const at::Tensor* norm_w = nullptr, double norm_eps = 0.0);
   void gated_overlap(int comm, at::Tensor A, at::Tensor B, at::Tensor C, at::Tensor D,
                      at::Tensor MM, at::Tensor RA, at::Tensor RE, int64_t rLDN,
                      at::Tensor cSEG_CPU, at::Tensor cSEG_GPU, int64_t Algo, bool monitor);
-  void ensure_fused_buffers(size_t stage_bytes, size_t nflags);
+  void ensure_fused_buffers(size_t stage_bytes, size_t nflags, bool pull);
   void ensure_comm_stream();
   cudaStream_t stream() const;
   ncclDataType_t nccl_dtype(const at::Tensor& t) const;
@@ -124,6 +131,8 @@ class OverlapImpl : public torch::CustomClassHolder {
   uint32_t epoch_ = 0;
   uint32_t a2a_epoch_ = 0;  // fused all-to-all calls so far (start-of-call handshake)
   at::Tensor a2a_tab_;      // device copy of the current call's row tables
+  at::Tensor norm_ssq_;     // fp32 [rows of the shard]: per-row sums of squares, zero between calls
+  at::Tensor norm_cnt_;     // int32 [row panels]: reduced tiles per panel, zero between calls
   at::Tensor status_;  // int32[kStatusWords] on the device
 
   int64_t opt_mode_ = 0;

@@ -226,6 +226,27 @@ def test_gemm_all2all_loopback(cuda, ws, algo, dt):
             assert (out[r][:n].float() - want[r]).abs().max().item() <= _tol(want[r]), r
 
 
+@experimental
+@pytest.mark.parametrize("ws,algo,strided,dt", [(2, 0, True, torch.bfloat16), (4, 2, False, torch.bfloat16),
+                                               (8, 0, True, torch.float16)])
+def test_reducescatter_rmsnorm_tail_loopback(cuda, ws, algo, strided, dt):
+    """Reducers that also normalise: out = rmsnorm(reduce_scatter(A B^T)) * w, no norm kernel."""
+    M, N, K = 1024, 2048, 256
+    BM = config.algo_params(algo)["BM"]
+    A = [_rand((M, K), dt, cuda) for _ in range(ws)]
+    B = [_rand((N, K), dt, cuda) for _ in range(ws)]
+    w = (1 + 0.1 * torch.randn(N, device=cuda)).to(dt)
+    full = sum(a.float() @ b.float().t() for a, b in zip(A, B))
+    out = [torch.full((M // ws, N), float("nan"), device=cuda, dtype=dt) for _ in range(ws)]
+    st = ops.fused_loopback("reduce_scatter", A, B, out, algo=algo, strided_rows=strided, natural_out=True,
+                            repeat=2, timeout_ms=2000, norm_w=w, norm_eps=1e-5)
+    assert all(s[0] == 0 for s in st), st
+    for r in range(ws):
+        shard = full[layout.owned_rows(M, BM, ws, r, strided).to(cuda)].to(dt)     # what the reducers round to
+        expect = layout.rmsnorm_ref(shard, w, 1e-5).float()
+        assert (out[r].float() - expect).abs().max().item() <= 0.03 * expect.abs().max().item(), r
+
+
 def test_fused_loopback_eight_ranks(cuda):
     """Eight ranks (16 owned rows per tile each), 18 CTAs per rank, on one GPU."""
     _loopback_case(cuda, "all_reduce", 8, 2048, 2048, 256, 0, True, False, repeat=2)

@@ -190,6 +190,35 @@ def test_gemm_all2all_fused_multi_gpu(lib):
             assert v <= 1.0, (k, v)
 
 
+def _norm_tail_worker(rank, world):
+    from flashoverlap_b200 import ops
+    dev = torch.device("cuda", rank)
+    impl = _setup(rank, world)
+    res = {}
+    for (M, N, K, algo) in ((1024, 2048, 512, 0), (2048, 2048, 512, 1), (2048, 4096, 256, 23)):
+        A, B = _rand((M, K), dev, 70 + rank), _rand((N, K), dev, 80 + rank)
+        w = (1 + 0.1 * _rand((N,), dev, 5, scale=1.0).float()).to(torch.bfloat16)
+        D = torch.empty(M // world, N, device=dev, dtype=torch.bfloat16)
+        impl.gemm_reducescatter_fused(A, B, D, algo)
+        expect = ops.rmsnorm(D, w, 1e-5).float()
+        Y = torch.full_like(D, float("nan"))
+        for _ in range(3):
+            impl.gemm_reducescatter_rmsnorm_fused(A, B, Y, w, 1e-5, algo)
+        torch.cuda.synchronize(); dist.barrier()
+        res[f"rs_norm_{algo}"] = (Y.float() - expect).abs().max().item() / (0.02 * expect.abs().max().item())
+    res["status"] = impl.read_status()[0]
+    return res
+
+
+@experimental
+def test_reducescatter_rmsnorm_tail_multi_gpu(lib):
+    world = _world()
+    for r in run_ranks(_norm_tail_worker, world, "nccl"):
+        assert r.pop("status") == 0
+        for k, v in r.items():
+            assert v <= 1.0, (k, v)
+
+
 def _api_worker(rank, world):
     from flashoverlap_b200 import ops
     from flashoverlap_b200.parallel import bootstrap
