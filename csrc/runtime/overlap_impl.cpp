@@ -184,6 +184,8 @@ void OverlapImpl::CheckStatus() {
 void OverlapImpl::ResetStatus() {
   FO_CHECK(status_.defined(), "call nccl_init first");
   status_.zero_();
+  if (norm_ssq_.defined()) norm_ssq_.zero_();  // an aborted call may have left partial statistics
+  if (norm_cnt_.defined()) norm_cnt_.zero_();
   if (signal_ != nullptr) {
     char* base = static_cast<char*>(signal_->local());
     cuda_check(cudaMemsetAsync(base + kSignalLocalCntOffset, 0, 128, stream()), "cudaMemsetAsync");
