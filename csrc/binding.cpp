@@ -193,6 +193,7 @@ TORCH_LIBRARY(flashoverlap_class, m) {
       .def("symm_empty", &OverlapImpl::SymmEmpty)
       .def("register_symmetric", &OverlapImpl::RegisterSymmetric)
       .def("use_stage", &OverlapImpl::UseStage)
+      .def("set_trace", &OverlapImpl::SetTrace)
       .def("read_status", &OverlapImpl::ReadStatus)
       .def("check_status", &OverlapImpl::CheckStatus)
       .def("reset_status", &OverlapImpl::ResetStatus);

@@ -86,6 +86,18 @@ FO_DEVICE bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // with 2 cycles per nanosecond (the SM clock never exceeds 2 GHz), so a wait lasts at least
 // as long as asked and at most about twice as long when the clock is throttled.
 FO_DEVICE uint64_t cycles_now() { return static_cast<uint64_t>(clock64()); }
+
+// Nanosecond clock shared by all SMs of a GPU (about a microsecond per read: tracing only).
+FO_DEVICE uint64_t globaltimer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+FO_DEVICE uint32_t sm_id() {
+  uint32_t v;
+  asm volatile("mov.u32 %0, %%smid;" : "=r"(v));
+  return v;
+}
 FO_DEVICE uint64_t ns_to_cycles(uint64_t ns) { return ns * 2ull; }
 
 // Bounded mbarrier wait.  `abort_flag` is a CTA-shared word any role sets when it gives

@@ -31,10 +31,11 @@ EncodeFn get_encode_fn() {
 }
 
 // query != nullptr: do not launch, report the largest co-resident grid instead.
-template <int BN, int STAGES, bool BF16, bool FUSED, bool CTA2, int MT = 1, bool A2A = false, bool NORM = false>
+template <int BN, int STAGES, bool BF16, bool FUSED, bool CTA2, int MT = 1, bool A2A = false, bool NORM = false,
+          bool TRACE = false>
 cudaError_t launch_one(const GemmTensorMaps* maps, const GemmParams* p, int grid_x, int nvr,
                        bool cooperative, cudaStream_t stream, int* query) {
-  auto kernel = fo_gemm_kernel<BN, STAGES, BF16, FUSED, CTA2, MT, A2A, NORM>;
+  auto kernel = fo_gemm_kernel<BN, STAGES, BF16, FUSED, CTA2, MT, A2A, NORM, TRACE>;
   constexpr int smem = GemmSmem<BN, STAGES, CTA2, MT>::kTotalBytes;
   static bool attr_set[16] = {};
   int dev = 0;
@@ -84,14 +85,14 @@ cudaError_t launch_one(const GemmTensorMaps* maps, const GemmParams* p, int grid
   return cudaLaunchKernelEx(&cfg, kernel, *maps, *p);
 }
 
-template <bool BF16, bool FUSED, bool A2A = false, bool NORM = false>
+template <bool BF16, bool FUSED, bool A2A = false, bool NORM = false, bool TRACE = false>
 cudaError_t launch_kernel_index(int kidx, const GemmTensorMaps* maps, const GemmParams* p,
                                 int grid_x, int nvr, bool coop, cudaStream_t s, int* query) {
   switch (kidx) {
-    case 0: return launch_one<256, 4, BF16, FUSED, false, 1, A2A, NORM>(maps, p, grid_x, nvr, coop, s, query);
-    case 1: return launch_one<256, 6, BF16, FUSED, true, 1, A2A, NORM>(maps, p, grid_x, nvr, coop, s, query);
-    case 2: return launch_one<128, 6, BF16, FUSED, false, 1, A2A, NORM>(maps, p, grid_x, nvr, coop, s, query);
-    default: return launch_one<256, 4, BF16, FUSED, true, 2, A2A, NORM>(maps, p, grid_x, nvr, coop, s, query);
+    case 0: return launch_one<256, 4, BF16, FUSED, false, 1, A2A, NORM, TRACE>(maps, p, grid_x, nvr, coop, s, query);
+    case 1: return launch_one<256, 6, BF16, FUSED, true, 1, A2A, NORM, TRACE>(maps, p, grid_x, nvr, coop, s, query);
+    case 2: return launch_one<128, 6, BF16, FUSED, false, 1, A2A, NORM, TRACE>(maps, p, grid_x, nvr, coop, s, query);
+    default: return launch_one<256, 4, BF16, FUSED, true, 2, A2A, NORM, TRACE>(maps, p, grid_x, nvr, coop, s, query);
   }
 }
 
@@ -105,6 +106,10 @@ cudaError_t dispatch(int algo, bool bf16, bool fused, const GemmTensorMaps* maps
   if (fused && p != nullptr && p->norm_w != nullptr) {  // reduce-scatter with the RMSNorm tail
     if (bf16) return launch_kernel_index<true, true, false, true>(kidx, maps, p, grid_x, nvr, coop, s, query);
     return launch_kernel_index<false, true, false, true>(kidx, maps, p, grid_x, nvr, coop, s, query);
+  }
+  if (fused && p != nullptr && p->trace != nullptr) {  // timeline-recording build of the fused kernel
+    if (bf16) return launch_kernel_index<true, true, false, false, true>(kidx, maps, p, grid_x, nvr, coop, s, query);
+    return launch_kernel_index<false, true, false, false, true>(kidx, maps, p, grid_x, nvr, coop, s, query);
   }
   if (bf16) {
     if (fused) return launch_kernel_index<true, true>(kidx, maps, p, grid_x, nvr, coop, s, query);

@@ -97,6 +97,21 @@ struct GemmParams {
   const void* norm_w;
   float* row_ssq;
   int* panel_cnt;
+  // Timeline of the fused kernels (tracing builds of the kernel only): [virtual rank][tile]
+  // [kTraceSlots] nanosecond stamps, see TraceSlot.  nullptr: no tracing.
+  unsigned long long* trace;
+};
+
+constexpr int kTraceSlots = 8;
+enum TraceSlot : int {
+  kTraceAccReady = 0,     // epilogue: the tile's accumulator is complete (main loop done)
+  kTraceEpilogueDone = 1, // epilogue: last chunk handed to the push warp
+  kTracePushIssued = 2,   // push warp: last store of the tile issued
+  kTraceSignalled = 3,    // push warp: stores complete, owners' arrival counters bumped
+  kTraceWaitBegin = 4,    // reducer: starts waiting for the tile's arrivals
+  kTraceWaitEnd = 5,      // reducer: every rank's slice has arrived
+  kTraceReduced = 6,      // reducer: reduction of the tile issued completely
+  kTraceWhere = 7,        // (SM id << 32) | CTA index
 };
 
 // ------------------------------------------------------------------ Algo table

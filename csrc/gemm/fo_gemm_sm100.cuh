@@ -421,11 +421,19 @@ __device__ __forceinline__ void reduce_tile_pull(const GemmParams& p, int me, in
   }
 }
 
-template <int BN, int STAGES, bool BF16, bool FUSED, bool CTA2, int MT, bool A2A = false, bool NORM = false>
+template <int BN, int STAGES, bool BF16, bool FUSED, bool CTA2, int MT, bool A2A = false, bool NORM = false,
+          bool TRACE = false>
 __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
     fo_gemm_kernel(const __grid_constant__ GemmTensorMaps maps,
                    const __grid_constant__ GemmParams p) {
   static_assert(!NORM || FUSED, "the RMSNorm tail belongs to the fused reduce-scatter");
+  static_assert(!TRACE || (FUSED && !NORM), "the timeline is recorded by the fused AR/RS kernels");
+  // Stamp slot `slot` of natural tile t (tracing builds only).
+  auto stamp = [&](int t, int slot) {
+    if constexpr (TRACE) {
+      p.trace[(static_cast<size_t>(blockIdx.y) * p.num_tiles + t) * kTraceSlots + slot] = ptx::globaltimer_ns();
+    }
+  };
   static_assert(MT == 1 || (MT == 2 && CTA2 && BN == 256), "two row halves need CTA pairs and BN = 256");
   static_assert(!(A2A && FUSED), "the all-to-all epilogue is a variant of the plain kernel");
   using L = GemmSmem<BN, STAGES, CTA2, MT>;
@@ -712,6 +720,13 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
       tc.m += h;
       const int t = tc.m * p.tiles_n + tc.n;
       const int r = (p.RA != nullptr) ? p.RA[t] : t;
+      if constexpr (TRACE) {
+        if (et == 0) {
+          stamp(t, kTraceAccReady);
+          p.trace[(static_cast<size_t>(blockIdx.y) * p.num_tiles + t) * kTraceSlots + kTraceWhere] =
+              (static_cast<unsigned long long>(ptx::sm_id()) << 32) | blockIdx.x;
+        }
+      }
 
       // Per-thread destinations for the cooperative store phase: thread `et` stores the
       // 16-byte piece (et & 7) of rows (et >> 3) + 16 * i, i = 0..7.
@@ -820,6 +835,7 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
 
       if constexpr (FUSED) {
         // arrival counters are bumped by the push warp
+        if (et == 0) stamp(t, kTraceEpilogueDone);
       } else {
         // All of this tile's stores have been issued by every epilogue thread.
         ptx::named_bar_sync(1, kEpilogueThreads);
@@ -890,6 +906,7 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
           int g, need;
           group_of_position(p, r, &g, &need);
           uint32_t obs;
+          stamp(t, kTraceWaitBegin);
           const uint32_t target = (p.diag & 4) ? 0u : static_cast<uint32_t>(need * ws);
           int ok = ptx::wait_counter_ge<true>(p.flags[me] + g, target, p.timeout_ns, s_abort, &obs)
                        ? 1
@@ -899,6 +916,7 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
             *s_abort = 1;
           }
           s_red_ok[slot] = ok;
+          stamp(t, kTraceWaitEnd);
         }
         ptx::named_bar_sync(2, kReducerThreads);
         if (!s_red_ok[slot]) break;
@@ -964,6 +982,7 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
             case 4: reduce_tile_pull<BN, BF16, 4>(p, me, rt, tile_off, out_base, out_ld); break;
             default: reduce_tile_pull<BN, BF16, 8>(p, me, rt, tile_off, out_base, out_ld); break;
           }
+          if (rt == 0) stamp(t, kTraceReduced);
           continue;
         }
         switch (ws) {
@@ -971,6 +990,7 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
           case 4: reduce_tile<BN, BF16, 4>(p, me, rt, src_tile, stride_b, out_base, out_ld); break;
           default: reduce_tile<BN, BF16, 8>(p, me, rt, src_tile, stride_b, out_base, out_ld); break;
         }
+        if (rt == 0) stamp(t, kTraceReduced);
       }
 
       // End-of-call handshake.  The last CTA of this rank to finish clears the group flags
@@ -1012,6 +1032,7 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
         const uint8_t* epi = smem + L::kEpiOffset;
         const int lag = p.push_lag < 1 ? 1 : (p.push_lag > kMaxLag ? kMaxLag : p.push_lag);
         int ring[kMaxLag];       // wave groups of the tiles whose pushes may still be in flight
+        int ring_t[TRACE ? kMaxLag : 1];  // their tile ids (tracing builds only)
         int ring_head = 0, ring_count = 0;
         uint32_t chunk_no = 0;
         bool ok = true;
@@ -1066,6 +1087,7 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
             ptx::mbar_arrive(&chunk_free_bar[b]);
           }
           if (!ok) break;
+          stamp(t, kTracePushIssued);
           int g, need;
           group_of_position(p, r, &g, &need);
           if (ring_count == lag) {
@@ -1078,10 +1100,12 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
               default: ptx::bulk_wait_group<kChunks * 4>(); break;
             }
             signal_group(ring[ring_head]);
+            if constexpr (TRACE) stamp(ring_t[ring_head], kTraceSignalled);
             ring_head = (ring_head + 1) % kMaxLag;
             --ring_count;
           }
           ring[(ring_head + ring_count) % kMaxLag] = g;
+          if constexpr (TRACE) ring_t[(ring_head + ring_count) % kMaxLag] = t;
           ++ring_count;
         }
         // Flush: every push must have landed before it is announced, and no bulk copy may
@@ -1089,6 +1113,7 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
         ptx::bulk_wait_group<0>();
         while (ring_count > 0) {
           signal_group(ring[ring_head]);
+          if constexpr (TRACE) stamp(ring_t[ring_head], kTraceSignalled);
           ring_head = (ring_head + 1) % kMaxLag;
           --ring_count;
         }

@@ -16,7 +16,8 @@ std::vector<int64_t> fused_loopback(std::string comm_op, std::vector<at::Tensor>
                                     bool strided_rows, bool natural_out, int64_t repeat,
                                     int64_t timeout_ms, bool stage_local,
                                     c10::optional<at::Tensor> mlen_opt,
-                                    c10::optional<at::Tensor> norm_w, double norm_eps) {
+                                    c10::optional<at::Tensor> norm_w, double norm_eps,
+                                    c10::optional<at::Tensor> trace) {
   const at::Tensor RA = RA_opt.has_value() ? *RA_opt : at::Tensor();
   const at::Tensor cseg_gpu = cseg_opt.has_value() ? *cseg_opt : at::Tensor();
   const int ws = static_cast<int>(A.size());
@@ -99,6 +100,13 @@ std::vector<int64_t> fused_loopback(std::string comm_op, std::vector<at::Tensor>
   if (a2a) {
     p.out_mode = kOutAll2All;
     p.a2a_tab = tab.data_ptr<int>();
+  }
+  if (trace.has_value() && trace->numel() > 0) {
+    FO_CHECK(!a2a && !norm_w.has_value(), "the timeline is recorded by the fused AllReduce / ReduceScatter kernels");
+    FO_CHECK(trace->is_cuda() && trace->is_contiguous() && trace->scalar_type() == at::kLong &&
+                 trace->numel() >= static_cast<int64_t>(ws) * p.num_tiles * kTraceSlots,
+             "trace must be a contiguous int64 CUDA tensor of ranks * tiles * 8 elements");
+    p.trace = reinterpret_cast<unsigned long long*>(trace->data_ptr<int64_t>());
   }
   at::Tensor row_ssq, panel_cnt;  // RMSNorm tail: statistics of every virtual rank
   if (norm_w.has_value()) {

@@ -166,6 +166,16 @@ void OverlapImpl::UseStage(at::Tensor buffer) {
   user_stage_ = reg;
 }
 
+void OverlapImpl::SetTrace(at::Tensor buffer) {
+  if (!buffer.defined() || buffer.numel() == 0) {
+    trace_ = at::Tensor();
+    return;
+  }
+  FO_CHECK(buffer.is_cuda() && buffer.is_contiguous() && buffer.scalar_type() == at::kLong,
+           "the trace buffer must be a contiguous int64 CUDA tensor");
+  trace_ = buffer;
+}
+
 std::vector<int64_t> OverlapImpl::ReadStatus() {
   FO_CHECK(status_.defined(), "call nccl_init first");
   at::Tensor h = status_.cpu();
@@ -429,6 +439,11 @@ void OverlapImpl::run_fused(int comm, const at::Tensor& A, const at::Tensor& B, 
     p.norm_eps = static_cast<float>(norm_eps);
     p.row_ssq = norm_ssq_.data_ptr<float>();
     p.panel_cnt = norm_cnt_.data_ptr<int>();
+  }
+  if (trace_.defined() && norm_w == nullptr) {
+    FO_CHECK(trace_.numel() >= static_cast<int64_t>(p.num_tiles) * kTraceSlots,
+             "the trace buffer needs ", static_cast<int64_t>(p.num_tiles) * kTraceSlots, " elements for this shape");
+    p.trace = reinterpret_cast<unsigned long long*>(trace_.data_ptr<int64_t>());
   }
   const SymmetricRegion* stage =
       (pull && user_stage_ != nullptr && user_stage_->bytes >= full_bytes) ? user_stage_ : stage_;

@@ -91,6 +91,13 @@ class OverlapImpl : public torch::CustomClassHolder {
   // least M*N*2 bytes.  When it carries a multicast mapping the owners' reducers sum the
   // partials with one switch-side reduction per vector (multimem.ld_reduce).  Same call on every rank.
   void UseStage(at::Tensor buffer);
+  // Timeline recording: while `buffer` (int64 CUDA tensor, at least tiles * 8 elements; an empty
+  // tensor switches recording off) is set, fused AllReduce / ReduceScatter calls run a build of
+  // the kernel that stamps, per 128-row tile, when its accumulator was complete, when the
+  // epilogue, the pushes and their completion signal were done and when the owner's reducer
+  // waited for, got and reduced it (layout: TraceSlot in gemm/fo_gemm_params.h;
+  // flashoverlap_b200/utils/trace.py turns it into a summary or a Chrome trace).
+  void SetTrace(at::Tensor buffer);
   // Status words written by device-side waits that gave up (all zero when healthy).
   std::vector<int64_t> ReadStatus();
   void CheckStatus();  // throws with a description when the status is not ok
@@ -131,6 +138,7 @@ class OverlapImpl : public torch::CustomClassHolder {
   uint32_t epoch_ = 0;
   uint32_t a2a_epoch_ = 0;  // fused all-to-all calls so far (start-of-call handshake)
   at::Tensor a2a_tab_;      // device copy of the current call's row tables
+  at::Tensor trace_;        // timeline buffer set by SetTrace, or undefined
   at::Tensor norm_ssq_;     // fp32 [rows of the shard]: per-row sums of squares, zero between calls
   at::Tensor norm_cnt_;     // int32 [row panels]: reduced tiles per panel, zero between calls
   at::Tensor status_;  // int32[kStatusWords] on the device

@@ -34,6 +34,9 @@ def main() -> None:
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--dtype", choices=["bf16", "fp16"], default="bf16")
+    ap.add_argument("--trace", default=None, metavar="FILE.json",
+                    help="fused kernels: record the per-tile timeline of one extra call, print its summary and "
+                         "write a Chrome trace of rank 0")
     ap.add_argument("--stage-local", action="store_true",
                     help="fused kernels: pull protocol (partials staged locally, owners fetch them)")
     a = ap.parse_args()
@@ -103,6 +106,13 @@ def main() -> None:
         res["tflops"] = round(flops / ms / 1e9, 1)
     if bytes_moved:
         res["gbs"] = round(bytes_moved / ms / 1e6, 1)
+    if a.trace and a.kernel in ("fused_ar", "fused_rs"):
+        from ..utils import trace
+        tiles = (M // BM) * (N // BN)
+        buf = trace.new_buffer(tiles, a.ranks, dev)
+        ops.fused_loopback(op, A, B, out, algo=a.algo, natural_out=True, stage_local=a.stage_local, trace=buf)
+        res["timeline_us"] = {k: {kk: round(vv, 2) for kk, vv in v.items()} for k, v in trace.summarize(buf, tiles).items()}
+        trace.to_chrome_trace(buf, tiles, a.trace)
     print(json.dumps(res))
 
 

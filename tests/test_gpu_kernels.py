@@ -247,6 +247,29 @@ def test_reducescatter_rmsnorm_tail_loopback(cuda, ws, algo, strided, dt):
         assert (out[r].float() - expect).abs().max().item() <= 0.03 * expect.abs().max().item(), r
 
 
+@experimental
+def test_fused_loopback_timeline(cuda):
+    """The tracing build of the fused kernel stamps every tile in order of its life cycle."""
+    from flashoverlap_b200.utils import trace
+    ws, M, N, K, algo = 2, 1024, 2048, 512, 0
+    p = config.algo_params(algo)
+    tiles = (M // p["BM"]) * (N // p["BN"])
+    A = [_rand((M, K), torch.bfloat16, cuda) for _ in range(ws)]
+    B = [_rand((N, K), torch.bfloat16, cuda) for _ in range(ws)]
+    out = [torch.empty(M, N, device=cuda, dtype=torch.bfloat16) for _ in range(ws)]
+    buf = trace.new_buffer(tiles, ws, cuda)
+    st = ops.fused_loopback("all_reduce", A, B, out, algo=algo, natural_out=True, trace=buf)
+    assert all(s[0] == 0 for s in st), st
+    full = sum(a.float() @ b.float().t() for a, b in zip(A, B))
+    assert (out[0].float() - full).abs().max().item() <= _tol(full)
+    t = buf.cpu().view(ws, tiles, trace.SLOTS)
+    assert (t[:, :, :7] > 0).all()
+    for a, b in ((0, 1), (1, 2), (2, 3), (4, 5), (5, 6), (3, 5)):     # signalled before the owner sees it
+        assert (t[:, :, b] >= t[:, :, a]).all(), (a, b)
+    s = trace.summarize(buf, tiles, rank=1)
+    assert s["reduce"]["tiles"] == tiles and s["span"]["us"] > 0
+
+
 def test_fused_loopback_eight_ranks(cuda):
     """Eight ranks (16 owned rows per tile each), 18 CTAs per rank, on one GPU."""
     _loopback_case(cuda, "all_reduce", 8, 2048, 2048, 256, 0, True, False, repeat=2)
