@@ -32,11 +32,12 @@ EncodeFn get_encode_fn() {
 
 // query != nullptr: do not launch, report the largest co-resident grid instead.
 template <int BN, int STAGES, bool BF16, bool FUSED, bool CTA2, int MT = 1, bool A2A = false, bool NORM = false,
-          bool TRACE = false>
+          bool TRACE = false, int EPI = 2>
 cudaError_t launch_one(const GemmTensorMaps* maps, const GemmParams* p, int grid_x, int nvr,
                        bool cooperative, cudaStream_t stream, int* query) {
-  auto kernel = fo_gemm_kernel<BN, STAGES, BF16, FUSED, CTA2, MT, A2A, NORM, TRACE>;
-  constexpr int smem = GemmSmem<BN, STAGES, CTA2, MT>::kTotalBytes;
+  auto kernel = fo_gemm_kernel<BN, STAGES, BF16, FUSED, CTA2, MT, A2A, NORM, TRACE, EPI>;
+  constexpr int smem = GemmSmem<BN, STAGES, CTA2, MT, EPI>::kTotalBytes;
+  static_assert(smem <= 227 * 1024, "shared memory of this configuration exceeds 227 KB");
   static bool attr_set[16] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -96,9 +97,25 @@ cudaError_t launch_kernel_index(int kidx, const GemmTensorMaps* maps, const Gemm
   }
 }
 
+// Fused kernels with four epilogue chunk buffers, paid for with one operand stage.
+template <bool BF16>
+cudaError_t launch_epi4(int kidx, const GemmTensorMaps* maps, const GemmParams* p, int grid_x, int nvr,
+                        bool coop, cudaStream_t s, int* query) {
+  switch (kidx) {
+    case 0: return launch_one<256, 3, BF16, true, false, 1, false, false, false, 4>(maps, p, grid_x, nvr, coop, s, query);
+    case 1: return launch_one<256, 5, BF16, true, true, 1, false, false, false, 4>(maps, p, grid_x, nvr, coop, s, query);
+    case 2: return launch_one<128, 5, BF16, true, false, 1, false, false, false, 4>(maps, p, grid_x, nvr, coop, s, query);
+    default: return launch_one<256, 3, BF16, true, true, 2, false, false, false, 4>(maps, p, grid_x, nvr, coop, s, query);
+  }
+}
+
 cudaError_t dispatch(int algo, bool bf16, bool fused, const GemmTensorMaps* maps, const GemmParams* p,
                      int grid_x, int nvr, bool coop, cudaStream_t s, int* query) {
   const int kidx = algo & 3;
+  if (fused && p != nullptr && p->epi_bufs == 4 && p->norm_w == nullptr && p->trace == nullptr) {
+    return bf16 ? launch_epi4<true>(kidx, maps, p, grid_x, nvr, coop, s, query)
+                : launch_epi4<false>(kidx, maps, p, grid_x, nvr, coop, s, query);
+  }
   if (p != nullptr && p->comm == kCommFusedA2A) {
     if (bf16) return launch_kernel_index<true, false, true>(kidx, maps, p, grid_x, nvr, coop, s, query);
     return launch_kernel_index<false, false, true>(kidx, maps, p, grid_x, nvr, coop, s, query);

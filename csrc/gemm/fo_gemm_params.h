@@ -100,6 +100,9 @@ struct GemmParams {
   // Timeline of the fused kernels (tracing builds of the kernel only): [virtual rank][tile]
   // [kTraceSlots] nanosecond stamps, see TraceSlot.  nullptr: no tracing.
   unsigned long long* trace;
+  // Fused kernels: 4 selects the build with four epilogue chunk buffers (and one operand stage
+  // fewer), whose push warp keeps three chunks of stores in flight; anything else the default (2).
+  int epi_bufs;
 };
 
 constexpr int kTraceSlots = 8;

@@ -51,7 +51,7 @@
 
 namespace fo {
 
-template <int BN, int STAGES, bool CTA2 = false, int MT = 1>
+template <int BN, int STAGES, bool CTA2 = false, int MT = 1, int EPI = 2>
 struct GemmSmem {
   static constexpr int kAHalfBytes = kBM * kBK * 2;
   static constexpr int kABytes = MT * kAHalfBytes;
@@ -61,8 +61,8 @@ struct GemmSmem {
   static constexpr int kEpiBufBytes = kBM * 128;  // 128 rows x 64 16-bit columns
   static constexpr int kRingBytes = STAGES * kStageBytes;
   static constexpr int kEpiOffset = kRingBytes;
-  static constexpr int kBarOffset = kEpiOffset + 2 * kEpiBufBytes;
-  static constexpr int kNumBars = 2 * STAGES + 4 + 4;  // + chunk_ready[2], chunk_free[2]
+  static constexpr int kBarOffset = kEpiOffset + EPI * kEpiBufBytes;  // EPI epilogue chunk buffers
+  static constexpr int kNumBars = 2 * STAGES + 4 + 2 * EPI;  // + chunk_ready[EPI], chunk_free[EPI]
   static constexpr int kMiscOffset = kBarOffset + kNumBars * 8;
   static constexpr int kMiscBytes = 64;
   // +1024: the ring is aligned up to 1024 B at run time (128-byte swizzle atom).
@@ -422,7 +422,7 @@ __device__ __forceinline__ void reduce_tile_pull(const GemmParams& p, int me, in
 }
 
 template <int BN, int STAGES, bool BF16, bool FUSED, bool CTA2, int MT, bool A2A = false, bool NORM = false,
-          bool TRACE = false>
+          bool TRACE = false, int EPI = 2>
 __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
     fo_gemm_kernel(const __grid_constant__ GemmTensorMaps maps,
                    const __grid_constant__ GemmParams p) {
@@ -436,7 +436,8 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
   };
   static_assert(MT == 1 || (MT == 2 && CTA2 && BN == 256), "two row halves need CTA pairs and BN = 256");
   static_assert(!(A2A && FUSED), "the all-to-all epilogue is a variant of the plain kernel");
-  using L = GemmSmem<BN, STAGES, CTA2, MT>;
+  static_assert(EPI == 2 || (FUSED && EPI >= 3), "more than two chunk buffers only pay in the fused kernels");
+  using L = GemmSmem<BN, STAGES, CTA2, MT, EPI>;
   // Accumulator slots in TMEM: two tiles in flight (MT = 1) or the two halves of one (MT = 2).
   constexpr int kAccStages = MT == 2 ? 1 : 2;
   extern __shared__ uint8_t smem_raw[];
@@ -450,7 +451,7 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
   uint64_t* tmem_full_bar = bars + 2 * STAGES;
   uint64_t* tmem_empty_bar = bars + 2 * STAGES + 2;
   uint64_t* chunk_ready_bar = bars + 2 * STAGES + 4;  // epilogue -> push warp: chunk written
-  uint64_t* chunk_free_bar = bars + 2 * STAGES + 6;   // push warp -> epilogue: chunk buffer reusable
+  uint64_t* chunk_free_bar = chunk_ready_bar + EPI;   // push warp -> epilogue: chunk buffer reusable
   uint32_t* misc = reinterpret_cast<uint32_t*>(smem + L::kMiscOffset);
   uint32_t* s_tmem_base = misc;                                   // written by tcgen05.alloc
   volatile int* s_abort = reinterpret_cast<volatile int*>(misc + 1);
@@ -492,6 +493,8 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
       ptx::mbar_init(&tmem_full_bar[i], 1);
       // one arrival per epilogue warp, from both CTAs of a pair
       ptx::mbar_init(&tmem_empty_bar[i], CTA2 ? 8 : 4);
+    }
+    for (int i = 0; i < EPI; ++i) {
       ptx::mbar_init(&chunk_ready_bar[i], kEpilogueThreads);
       ptx::mbar_init(&chunk_free_bar[i], 1);
     }
@@ -789,12 +792,12 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
           // The buffer is free once the push warp's stores of its previous use have read it.
           // A failed wait raises the abort flag but the thread stays in step with the others:
           // everybody leaves together at the next tile boundary.
-          if (!ptx::mbar_wait_bounded(&chunk_free_bar[chunk_no & 1], ((chunk_no >> 1) & 1u) ^ 1u, s_abort,
+          if (!ptx::mbar_wait_bounded(&chunk_free_bar[chunk_no % EPI], ((chunk_no / EPI) & 1u) ^ 1u, s_abort,
                                       pipe_timeout)) {
             *s_abort = 1;
           }
         }
-        const int bsel = FUSED ? static_cast<int>(chunk_no & 1u) : (c & 1);
+        const int bsel = FUSED ? static_cast<int>(chunk_no % EPI) : (c & 1);
         uint8_t* buf = epi + bsel * L::kEpiBufBytes + smem_row * 128;
         const int sw = smem_row & 7;
 #pragma unroll
@@ -818,7 +821,7 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
         if constexpr (FUSED) {
           // Hand the chunk to the push warp (generic-proxy writes ordered before its TMA reads).
           ptx::fence_proxy_async_smem();
-          ptx::mbar_arrive(&chunk_ready_bar[chunk_no & 1]);
+          ptx::mbar_arrive(&chunk_ready_bar[chunk_no % EPI]);
           ++chunk_no;
         } else {
           ptx::named_bar_sync(1, kEpilogueThreads);
@@ -1065,8 +1068,8 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
           const int r = (p.RA != nullptr) ? p.RA[t] : t;
           const int row0 = (me * p.num_tiles + t) * rows_owned;
           for (int c = 0; c < kChunks; ++c, ++chunk_no) {
-            const int b = static_cast<int>(chunk_no & 1u);
-            if (!ptx::mbar_wait_bounded(&chunk_ready_bar[b], (chunk_no >> 1) & 1u, s_abort, pipe_timeout)) {
+            const int b = static_cast<int>(chunk_no % EPI);
+            if (!ptx::mbar_wait_bounded(&chunk_ready_bar[b], (chunk_no / EPI) & 1u, s_abort, pipe_timeout)) {
               ptx::report_status(status, kStatusTimeoutTmemFull, pos, c, 1);
               *s_abort = 1;
               ok = false;
@@ -1083,8 +1086,17 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
               }
             }
             ptx::bulk_commit_group();
-            ptx::bulk_wait_group_read<0>();     // sources read: the epilogue may refill the buffer
-            ptx::mbar_arrive(&chunk_free_bar[b]);
+            if constexpr (EPI == 2) {
+              ptx::bulk_wait_group_read<0>();     // sources read: the epilogue may refill the buffer
+              ptx::mbar_arrive(&chunk_free_bar[b]);
+            } else {
+              // More buffers: keep EPI - 1 chunks of stores in flight and hand back the buffer of
+              // the chunk issued EPI - 1 chunks ago, whose stores have read their source by now.
+              ptx::bulk_wait_group_read<EPI - 1>();
+              if (chunk_no >= static_cast<uint32_t>(EPI - 1)) {
+                ptx::mbar_arrive(&chunk_free_bar[(chunk_no - static_cast<uint32_t>(EPI - 1)) % EPI]);
+              }
+            }
           }
           if (!ok) break;
           stamp(t, kTracePushIssued);

@@ -17,7 +17,8 @@ namespace fo {
 // is [M,N] (all_reduce), [M/ws,N] (reduce_scatter) or the receive buffer of rank r (all_to_all,
 // whose row counts come in the int32 host tensor mlen [ws, ws]).  With norm_w (reduce_scatter,
 // natural_out) the reducers apply the RMSNorm tail: out[r] = rmsnorm(shard) * norm_w.  trace: int64
-// CUDA tensor of ws * tiles * 8 elements that receives the timeline of the (last) call.  RA / cseg_gpu may be None
+// CUDA tensor of ws * tiles * 8 elements that receives the timeline of the (last) call.  epi_bufs:
+// 2 (default build) or 4 (four epilogue chunk buffers, one operand stage fewer).  RA / cseg_gpu may be None
 // (identity order / one flag per tile).  natural_out selects row-major results instead of
 // the tile-contiguous layout.  The call is repeated `repeat` times back to back to exercise
 // the call-to-call handshake.  stage_local selects the pull protocol (partials staged in the
@@ -31,6 +32,6 @@ std::vector<int64_t> fused_loopback(std::string comm_op, std::vector<at::Tensor>
                                     int64_t timeout_ms, bool stage_local,
                                     c10::optional<at::Tensor> mlen,
                                     c10::optional<at::Tensor> norm_w, double norm_eps,
-                                    c10::optional<at::Tensor> trace);
+                                    c10::optional<at::Tensor> trace, int64_t epi_bufs);
 
 }  // namespace fo

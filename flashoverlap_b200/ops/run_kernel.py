@@ -37,6 +37,8 @@ def main() -> None:
     ap.add_argument("--trace", default=None, metavar="FILE.json",
                     help="fused kernels: record the per-tile timeline of one extra call, print its summary and "
                          "write a Chrome trace of rank 0")
+    ap.add_argument("--epi-bufs", type=int, default=2, choices=[2, 4],
+                    help="fused kernels: epilogue chunk buffers (4 = build with one operand stage fewer)")
     ap.add_argument("--stage-local", action="store_true",
                     help="fused kernels: pull protocol (partials staged locally, owners fetch them)")
     a = ap.parse_args()
@@ -89,7 +91,8 @@ def main() -> None:
         out = [torch.empty(rows, N, device=dev, dtype=dt) for _ in range(ws)]
         op = "all_reduce" if a.kernel == "fused_ar" else "reduce_scatter"
         flops = 2.0 * M * N * K * ws
-        fn = lambda: ops.fused_loopback(op, A, B, out, algo=a.algo, natural_out=True, stage_local=a.stage_local)
+        fn = lambda: ops.fused_loopback(op, A, B, out, algo=a.algo, natural_out=True, stage_local=a.stage_local,
+                                        epi_bufs=a.epi_bufs)
 
     for _ in range(a.warmup):
         fn()
@@ -110,7 +113,7 @@ def main() -> None:
         from ..utils import trace
         tiles = (M // BM) * (N // BN)
         buf = trace.new_buffer(tiles, a.ranks, dev)
-        ops.fused_loopback(op, A, B, out, algo=a.algo, natural_out=True, stage_local=a.stage_local, trace=buf)
+        ops.fused_loopback(op, A, B, out, algo=a.algo, natural_out=True, stage_local=a.stage_local, trace=buf)  # default build
         res["timeline_us"] = {k: {kk: round(vv, 2) for kk, vv in v.items()} for k, v in trace.summarize(buf, tiles).items()}
         trace.to_chrome_trace(buf, tiles, a.trace)
     print(json.dumps(res))

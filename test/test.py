@@ -73,6 +73,10 @@ def worker(rank, world, args):
         if switch:
             res["fused_pull_switch_ms"] = perf_ms(wl.run, WARM_UP, args.reps, f)
         impl.set_option("stage_local", 0)
+    if world > 1 and args.epi4:
+        impl.set_option("epi_bufs", 4)
+        res["fused_epi4_ms"] = perf_ms(wl.run, WARM_UP, args.reps, f)
+        impl.set_option("epi_bufs", 2)
     if world > 1:
         wl.mode = "gated"
         wave = sm - margin
@@ -104,7 +108,8 @@ def worker(rank, world, args):
             print(f"{'overlap (gated NCCL)':>24} {res['gated_ms']:.4f} ms   speedup {res['speedup_gated']:.3f}")
         print(f"{'overlap (fused)':>24} {res['fused_ms']:.4f} ms   speedup {res['speedup_fused']:.3f}   "
               f"roofline {res['roofline_ms']:.4f} ms ({100 * res['roofline_frac']:.1f}% of measured peaks)")
-        for key, label in (("fused_pull_peer_ms", "fused, pull (peer loads)"), ("fused_pull_switch_ms", "fused, pull (switch sum)")):
+        for key, label in (("fused_pull_peer_ms", "fused, pull (peer loads)"), ("fused_pull_switch_ms", "fused, pull (switch sum)"),
+                           ("fused_epi4_ms", "fused, 4 chunk buffers")):
             if key in res:
                 print(f"{label:>24} {res[key]:.4f} ms   speedup {res['baseline_ms'] / res[key]:.3f}")
         print(json.dumps({k: (round(v, 5) if isinstance(v, float) else v) for k, v in res.items()}))
@@ -122,6 +127,8 @@ def main():
     ap.add_argument("--path", default=None)
     ap.add_argument("--reps", type=int, default=REP)
     ap.add_argument("--flush", action="store_true", help="flush L2 between timed iterations")
+    ap.add_argument("--epi4", action="store_true",
+                    help="also time the fused kernel built with four epilogue chunk buffers (option epi_bufs)")
     ap.add_argument("--pull", action="store_true",
                     help="also time the pull protocol of the fused kernel (option stage_local), with peer loads "
                          "and with the NVSwitch reduction")

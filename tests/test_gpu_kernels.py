@@ -162,7 +162,7 @@ def test_wait_flag_completes_and_times_out(cuda):
 
 
 def _loopback_case(cuda, comm_op, ws, M, N, K, algo, strided, natural, repeat=1, groups=None, dt=torch.bfloat16,
-                   stage_local=False):
+                   stage_local=False, epi_bufs=2):
     p = config.algo_params(algo)
     BM, BN = p["BM"], p["BN"]
     tiles = (M // BM) * (N // BN)
@@ -174,7 +174,8 @@ def _loopback_case(cuda, comm_op, ws, M, N, K, algo, strided, natural, repeat=1,
     rows = M if comm_op == "all_reduce" else M // ws
     out = [torch.full((rows, N), float("nan"), device=cuda, dtype=dt) for _ in range(ws)]
     st = ops.fused_loopback(comm_op, A, B, out, RA=RA, cseg=cseg, algo=algo, strided_rows=strided,
-                            natural_out=natural, repeat=repeat, timeout_ms=2000, stage_local=stage_local)
+                            natural_out=natural, repeat=repeat, timeout_ms=2000, stage_local=stage_local,
+                            epi_bufs=epi_bufs)
     assert all(s[0] == 0 for s in st), st
     for r in range(ws):
         if comm_op == "all_reduce":
@@ -268,6 +269,16 @@ def test_fused_loopback_timeline(cuda):
         assert (t[:, :, b] >= t[:, :, a]).all(), (a, b)
     s = trace.summarize(buf, tiles, rank=1)
     assert s["reduce"]["tiles"] == tiles and s["span"]["us"] > 0
+
+
+@experimental
+@pytest.mark.parametrize("comm_op", ["all_reduce", "reduce_scatter"])
+def test_fused_loopback_four_chunk_buffers(cuda, comm_op):
+    """Build with four epilogue chunk buffers: the push warp keeps three chunks of stores in flight."""
+    _loopback_case(cuda, comm_op, 2, 1024, 2048, 512, 0, True, True, epi_bufs=4)
+    _loopback_case(cuda, comm_op, 4, 1024, 2048, 256, 2, False, False, repeat=3, epi_bufs=4)
+    _loopback_case(cuda, comm_op, 8, 2048, 2048, 256, 0, True, False, repeat=2, epi_bufs=4)
+    _loopback_case(cuda, comm_op, 2, 2048, 2048, 128, 2, True, True, repeat=2, stage_local=True, epi_bufs=4)
 
 
 def test_fused_loopback_eight_ranks(cuda):
