@@ -39,6 +39,18 @@
 // the two accumulators fill TMEM, so a tile's epilogue no longer overlaps the next main loop.
 // Worth it when the main loop is long (K per rank in the several thousands).
 //
+// Compile-time variants (template flags; the default builds contain none of their code):
+//   A2A    plain kernel whose epilogue stores each row into the receive buffer of the rank it
+//          is bound for (fused GEMM + all-to-all), with start- and end-of-call handshakes;
+//   NORM   fused reduce-scatter whose reducers also gather each row's sum of squares and
+//          normalise a 128-row panel when its last tile has been reduced (RMSNorm tail);
+//   TRACE  fused kernels that stamp the life cycle of every tile for a timeline;
+//   EPI    number of epilogue chunk buffers of the fused kernels (2, or 4 with one operand
+//          stage fewer and three chunks of push stores in flight).
+// Run-time variant: the pull protocol (GemmParams::stage_local), where partial tiles stay in
+// the producing rank's staging buffer and the owners fetch them - with one multimem.ld_reduce
+// per vector when the staging has an NVSwitch multicast mapping.
+//
 // Every wait is bounded: on expiry the role records a status code, raises a CTA-wide abort
 // flag, the producer drains its TMA loads in flight, TMEM is freed and the kernel returns.
 #pragma once
