@@ -424,8 +424,6 @@ def extras(torch, dist, impl, rank, world, dev, A, B, C, algo, flush, peaks, ste
     rs["cublas_nccl_rmsnorm_ms"] = round(msb, 5)
     rs["speedup_vs_cublas_nccl"] = round(msb / ms, 4)
     out["rs_rmsnorm"] = rs
-    if "cublas_nccl_ms" in out:
-        pass
     impl.check_status()
     return out
 
