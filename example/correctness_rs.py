@@ -11,7 +11,6 @@ import argparse
 
 import _common  # noqa: F401
 import torch
-import torch.distributed as dist
 import torch.nn as nn
 
 from flashoverlap_b200.models import OverlapRowParallelLayer, ReorderRMSNorm, RMSNorm, RowParallelLayer

@@ -17,7 +17,6 @@ Two implementations of the same math:
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Optional
 
 import torch
 import torch.distributed as dist

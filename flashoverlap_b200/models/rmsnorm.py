@@ -6,7 +6,7 @@ overlapped GEMM and returns the row-major, normalised result in one pass over me
 """
 from __future__ import annotations
 
-from typing import Optional, Sequence
+from typing import Sequence
 
 import torch
 import torch.nn as nn

@@ -7,7 +7,6 @@ keep working, with optional extras.
 """
 from __future__ import annotations
 
-from typing import Optional
 
 import torch
 import torch.distributed as dist

@@ -3,7 +3,7 @@ launching stream around every iteration, mean per rank, maximum over ranks (the 
 protocol, test/test.py:112-119, :186-190), plus an optional L2 flush between iterations."""
 from __future__ import annotations
 
-from typing import Callable, Optional
+from typing import Callable
 
 import torch
 import torch.distributed as dist

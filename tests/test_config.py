@@ -3,7 +3,7 @@ import json
 
 import torch
 
-from flashoverlap_b200.utils import config, layout
+from flashoverlap_b200.utils import config
 
 
 def test_algo_table_matches_native(lib):

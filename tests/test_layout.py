@@ -1,5 +1,4 @@
 """Layout oracle: tile orders, reordered layout, reduce-scatter row maps (CPU)."""
-import itertools
 
 import pytest
 import torch

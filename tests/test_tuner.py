@@ -1,5 +1,4 @@
 """Latency model, candidate enumeration and search drivers of the wave-group tuner (CPU)."""
-import math
 
 import pytest
 import torch

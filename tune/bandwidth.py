@@ -20,7 +20,6 @@ import argparse
 
 from _common import config, dtype_of, torch
 
-import torch.distributed as dist
 
 from flashoverlap_b200 import tuner
 from flashoverlap_b200.parallel import bootstrap

@@ -19,7 +19,7 @@ scalars ``BM, BN, dur, Algo`` plus ``hint``, ``cSeg`` and ``rLDN`` (reference: t
 """
 import argparse
 
-from _common import OverlapWorkload, config, dtype_of, layout, str2bool, torch
+from _common import OverlapWorkload, config, dtype_of, str2bool, torch
 
 from flashoverlap_b200 import tuner
 from flashoverlap_b200.parallel import bootstrap
