@@ -111,7 +111,7 @@ def _pull_worker(rank, world):
     dev = torch.device("cuda", rank)
     impl = _setup(rank, world)
     impl.set_option("stage_local", 1)
-    switch_reduce = os.environ.get("FLASHOVERLAP_EXPERIMENTAL", "0") == "1"
+    switch_reduce = True
     res = {"info_switch_reduce": 0.0}
     for (M, N, K, algo) in ((1024, 2048, 512, 0), (2048, 2048, 512, 1), (2048, 1024, 256, 3)):
         BM = config.algo_params(algo)["BM"]
@@ -143,9 +143,10 @@ def _pull_worker(rank, world):
     return res
 
 
+@experimental
 def test_pull_protocol_multi_gpu(lib):
-    """With FLASHOVERLAP_EXPERIMENTAL=1 the staging also goes to multicast-mapped memory, where the
-    owners' reducers sum with multimem.ld_reduce."""
+    """Pull protocol over real NVLink: first with peer loads, then with the staging in
+    multicast-mapped memory, where the owners' reducers sum with multimem.ld_reduce."""
     world = _world()
     for r in run_ranks(_pull_worker, world, "nccl"):
         assert r.pop("status") == 0
