@@ -114,8 +114,23 @@ class ClockSampler:
         return out
 
 
-def pick_algo(torch, dist, world, run, candidates, reps=3):
-    """Fastest Algo by a short timing, agreed on by all ranks (max over ranks per candidate)."""
+def pick_algo(torch, dist, world, run, candidates, reps=10, settle_seconds=0.5):
+    """Fastest Algo by a short timing, agreed on by all ranks (max over ranks per candidate).
+    The candidates are ranked under load: a cold GPU runs all of them at boost clocks, while the
+    timed region runs at the power cap, where the kernels that move fewer bytes win."""
+    try:
+        run(candidates[0])
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        run(candidates[0])
+        torch.cuda.synchronize()
+        one = torch.tensor([max(time.perf_counter() - t0, 1e-5)], device="cuda")
+        if world > 1:
+            dist.all_reduce(one, op=dist.ReduceOp.MAX)       # same number of settling steps on every rank
+        for _ in range(int(min(1000, settle_seconds / one.item()))):
+            run(candidates[0])
+    except Exception:
+        pass
     times = []
     for a in candidates:
         try:
