@@ -104,3 +104,92 @@ def test_rmsnorm_tail_arithmetic(ws, dt):
     want = layout.rmsnorm_ref(partial.float().sum(0).to(dt), w, eps)
     # identical up to the order in which the fp32 squares are added
     assert (y.float() - want.float()).abs().max().item() <= 2 * torch.finfo(dt).eps * want.float().abs().max().item()
+
+
+class _RankState:
+    def __init__(self, ws, ctas, tiles):
+        self.flags = [0] * tiles                       # arrival counters of this rank (as owner)
+        self.done = 0                                  # ranks that have completed a call, cumulative
+        self.local_cnt = 0
+        self.stage = [[None] * tiles for _ in range(ws)]   # [source rank][tile] -> call that wrote it
+        self.call = 0                                  # call this rank's kernel is running (1-based), 0 = idle
+        self.cta = []
+
+
+@pytest.mark.parametrize("comm", ["all_reduce", "reduce_scatter"])
+@pytest.mark.parametrize("pull", [False, True])
+@pytest.mark.parametrize("seed", [0, 1, 2, 3])
+def test_cross_rank_counters_under_random_interleavings(comm, pull, seed):
+    """Arrival counters, `done` epochs, flag clearing by the last CTA and staging reuse over
+    several back-to-back calls, for the push protocol (partials stored into the owners' staging)
+    and the pull protocol (partials kept in the producer's staging, owners read them): every
+    reducer must find, for every tile, the partials of the CURRENT call from every rank, and
+    nobody may get stuck."""
+    rng = random.Random(seed)
+    ws, ctas, tiles, calls = 3, 4, 10, 3
+    ranks = [_RankState(ws, ctas, tiles) for _ in range(ws)]
+
+    def start_call(r):
+        st = ranks[r]
+        st.call += 1
+        my_tiles = lambda c: [t for t in range(tiles) if t % ctas == c]
+        st.cta = [{"push": {"tiles": my_tiles(c), "i": 0, "started": False},
+                   "red": {"tiles": my_tiles(c), "i": 0, "phase": "tiles"}} for c in range(ctas)]
+
+    for r in range(ws):
+        start_call(r)
+    consumed = 0
+    for _ in range(400000):
+        if all(st.call == calls and all(c["red"]["phase"] == "exit" for c in st.cta) for st in ranks):
+            break
+        r = rng.randrange(ws)
+        st = ranks[r]
+        if all(c["red"]["phase"] == "exit" for c in st.cta):
+            if st.call < calls:
+                start_call(r)                           # next kernel on this rank's stream
+            continue
+        c = st.cta[rng.randrange(ctas)]
+        epoch = st.call
+        if rng.random() < 0.5:
+            p = c["push"]
+            if not p["started"]:
+                if st.done >= ws * (epoch - 1):          # peers have consumed the previous call's staging
+                    p["started"] = True
+                continue
+            if p["i"] < len(p["tiles"]):
+                t = p["tiles"][p["i"]]
+                for o in range(ws):                      # stores complete, then the arrival is announced
+                    if pull:
+                        ranks[r].stage[r][t] = epoch     # own staging only; the owners will read it
+                    else:
+                        ranks[o].stage[r][t] = epoch
+                for o in range(ws):
+                    ranks[o].flags[t] += 1
+                p["i"] += 1
+        else:
+            q = c["red"]
+            if q["phase"] == "tiles":
+                if q["i"] == len(q["tiles"]):
+                    st.local_cnt += 1
+                    if st.local_cnt == ctas:             # last CTA of this rank
+                        st.flags = [0] * tiles
+                        st.local_cnt = 0
+                        for o in range(ws):
+                            ranks[o].done += 1
+                        q["phase"] = "wait_done" if comm == "all_reduce" else "exit"
+                    else:
+                        q["phase"] = "exit"
+                    continue
+                t = q["tiles"][q["i"]]
+                assert st.flags[t] <= ws, "an arrival of another call leaked into this one"
+                if st.flags[t] == ws:
+                    seen = [ranks[s].stage[s][t] if pull else st.stage[s][t] for s in range(ws)]
+                    assert all(v == epoch for v in seen), f"rank {r} tile {t}: staging holds calls {seen} in call {epoch}"
+                    consumed += 1
+                    q["i"] += 1
+            elif q["phase"] == "wait_done":
+                if st.done >= ws * epoch:
+                    q["phase"] = "exit"
+    else:
+        raise AssertionError("the protocol got stuck")
+    assert consumed == ws * tiles * calls
