@@ -193,3 +193,75 @@ def test_cross_rank_counters_under_random_interleavings(comm, pull, seed):
     else:
         raise AssertionError("the protocol got stuck")
     assert consumed == ws * tiles * calls
+
+
+@pytest.mark.parametrize("seed", [0, 1, 2, 3])
+def test_all2all_handshakes_under_random_interleavings(seed):
+    """Fused GEMM + all-to-all: `ready` counters (a receive buffer is written only after its owner
+    has entered the call, i.e. after its reader of the previous call) and `done` counters (the
+    kernel ends only when every rank has sent everything).  The reader that follows each kernel
+    on a rank's stream must see the rows of exactly that call from every peer."""
+    rng = random.Random(seed)
+    ws, ctas, calls = 3, 3, 4
+    recv = [[0] * ws for _ in range(ws)]        # recv[o][s]: call whose rows from s sit in o's buffer
+    ready = [0] * ws
+    done = [0] * ws
+    local_cnt = [0] * ws
+    state = [{"call": 0, "phase": "idle", "cta": []} for _ in range(ws)]
+
+    def start(r):
+        st = state[r]
+        st["call"] += 1
+        st["phase"] = "kernel"
+        st["cta"] = [{"step": "announce" if c == 0 else "wait_ready"} for c in range(ctas)]
+
+    for r in range(ws):
+        start(r)
+    reads = 0
+    for _ in range(200000):
+        if all(st["call"] == calls and st["phase"] == "finished" for st in state):
+            break
+        r = rng.randrange(ws)
+        st = state[r]
+        k = st["call"]
+        if st["phase"] == "read":                       # the consumer of this call's rows
+            for s in range(ws):
+                if s != r:
+                    assert recv[r][s] == k, f"rank {r} reads rows of call {recv[r][s]} from {s} in call {k}"
+            reads += 1
+            st["phase"] = "finished" if k == calls else "idle"
+            if st["phase"] == "idle":
+                start(r)
+            continue
+        if st["phase"] != "kernel":
+            continue
+        c = st["cta"][rng.randrange(ctas)]
+        if c["step"] == "announce":
+            for o in range(ws):
+                ready[o] += 1
+            c["step"] = "wait_ready"
+        elif c["step"] == "wait_ready":
+            if ready[r] >= ws * k:
+                c["step"] = "store"
+        elif c["step"] == "store":
+            for o in range(ws):
+                if o != r:
+                    assert state[o]["call"] == k and state[o]["phase"] == "kernel", \
+                        f"rank {r} writes call {k} into rank {o} which is in call {state[o]['call']} ({state[o]['phase']})"
+                    recv[o][r] = k
+            local_cnt[r] += 1
+            if local_cnt[r] == ctas:
+                local_cnt[r] = 0
+                for o in range(ws):
+                    done[o] += 1
+                c["step"] = "wait_done"
+            else:
+                c["step"] = "exit"
+        elif c["step"] == "wait_done":
+            if done[r] >= ws * k:
+                c["step"] = "exit"
+        if all(x["step"] == "exit" for x in st["cta"]):
+            st["phase"] = "read"
+    else:
+        raise AssertionError("the handshake got stuck")
+    assert reads == ws * calls
