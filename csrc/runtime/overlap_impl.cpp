@@ -99,6 +99,9 @@ void OverlapImpl::SetOption(std::string name, int64_t value) {
     opt_push_lag_ = value;
   } else if (name == "stage_local") {
     opt_stage_local_ = value ? 1 : 0;
+  } else if (name == "diag") {
+    FO_CHECK(value >= 0 && value <= 7, "diag is a bit mask of 1 | 2 | 4");
+    opt_diag_ = value;
   } else if (name == "epi_bufs") {
     FO_CHECK(value == 2 || value == 4, "epi_bufs must be 2 or 4");
     opt_epi_bufs_ = value;
@@ -117,6 +120,7 @@ int64_t OverlapImpl::GetOption(std::string name) {
   if (name == "push_lag") return opt_push_lag_;
   if (name == "stage_local") return opt_stage_local_;
   if (name == "epi_bufs") return opt_epi_bufs_;
+  if (name == "diag") return opt_diag_;
   if (name == "sm_count") return sm_count_;
   if (name == "rank") return rank_;
   if (name == "world") return world_;
@@ -453,6 +457,7 @@ void OverlapImpl::run_fused(int comm, const at::Tensor& A, const at::Tensor& B, 
       (pull && user_stage_ != nullptr && user_stage_->bytes >= full_bytes) ? user_stage_ : stage_;
   p.stage_local = pull ? 1 : 0;
   p.epi_bufs = static_cast<int>(opt_epi_bufs_);
+  p.diag = static_cast<int>(opt_diag_);
   if (pull && stage->multicast != nullptr && opt_nvls_ != 0) p.mc_stage = stage->multicast;
   for (int r = 0; r < world_; ++r) {
     p.stage[r] = stage->ptr[r];

@@ -76,7 +76,9 @@ class OverlapImpl : public torch::CustomClassHolder {
   // "stage_local" (1: pull protocol - partials stay in the producing rank's staging buffer and
   // the owners fetch them, through the switch's reduction when the buffer has a multicast mapping),
   // "epi_bufs" (2 | 4: fused kernels with four epilogue chunk buffers and one operand stage fewer;
-  // their push warp keeps three chunks of stores in flight instead of waiting for each).
+  // their push warp keeps three chunks of stores in flight instead of waiting for each),
+  // "diag" (timing studies only - results are wrong: 1 skips the reducers' memory traffic, 2 the
+  // push stores, 4 the reducers' arrival waits; shows which part of the collective is exposed).
   void SetOption(std::string name, int64_t value);
   int64_t GetOption(std::string name);
   // Collective allocation of a tensor in symmetric memory.  AllReduce results written into
@@ -151,6 +153,7 @@ class OverlapImpl : public torch::CustomClassHolder {
   int64_t opt_timeout_ms_ = 2000;
   int64_t opt_nvls_ = 1;      // use a registered multicast mapping when there is one
   int64_t opt_push_lag_ = 0;  // 0: chosen from K
+  int64_t opt_diag_ = 0;         // timing studies only (results are wrong): see GemmParams::diag
   int64_t opt_epi_bufs_ = 2;     // epilogue chunk buffers of the fused kernels (2 or 4)
   int64_t opt_stage_local_ = 0;  // 1: pull protocol (partials staged locally, owners fetch them)
   int64_t opt_l2_hints_ = 0;  // measured: priorities raise DRAM traffic on B200, off by default
