@@ -78,7 +78,9 @@ class OverlapImpl : public torch::CustomClassHolder {
   // "epi_bufs" (2 | 4: fused kernels with four epilogue chunk buffers and one operand stage fewer;
   // their push warp keeps three chunks of stores in flight instead of waiting for each),
   // "diag" (timing studies only - results are wrong: 1 skips the reducers' memory traffic, 2 the
-  // push stores, 4 the reducers' arrival waits; shows which part of the collective is exposed).
+  // push stores, 4 the reducers' arrival waits; shows which part of the collective is exposed.
+  // After runs with bit 4, synchronise all ranks and call reset_status() before normal calls:
+  // late arrivals may have been counted after the counters were cleared).
   void SetOption(std::string name, int64_t value);
   int64_t GetOption(std::string name);
   // Collective allocation of a tensor in symmetric memory.  AllReduce results written into
