@@ -376,10 +376,19 @@ def extras(torch, dist, impl, rank, world, dev, A, B, C, algo, flush, peaks, ste
     base = bootstrap.make_baseline_impl(rank, world)
     ms, _, _ = time_steps(torch, dist, world, lambda: base.gemm_allreduce(A, B, Cn), steps, warm, flush)
     out["cublas_nccl_ms"] = round(ms, 5)
-    ms, _, _ = time_steps(torch, dist, world, lambda: base.cublas_gemm(A, B, Cn), steps, warm, flush)
+    # The two bare GEMMs are timed with the clock sampler as well: under the power cap the SM clock
+    # each kernel sustains is what separates them.
+    def brief(c):
+        return None if not c else {"sm_mhz": c.get("sm_mhz"), "power_w_max": c.get("power_w_max"), "reasons": c.get("reasons")}
+
+    smp = ClockSampler(dev.index) if rank == 0 else None
+    ms, clk, _ = time_steps(torch, dist, world, lambda: base.cublas_gemm(A, B, Cn), steps, warm, flush, smp)
     out["cublas_gemm_only_ms"] = round(ms, 5)
-    ms, _, _ = time_steps(torch, dist, world, lambda: impl.cutlass_gemm(A, B, Cn, algo), steps, warm, flush)
+    out["cublas_gemm_only_clocks"] = brief(clk)
+    smp = ClockSampler(dev.index) if rank == 0 else None
+    ms, clk, _ = time_steps(torch, dist, world, lambda: impl.cutlass_gemm(A, B, Cn, algo), steps, warm, flush, smp)
     out["our_gemm_only_ms"] = round(ms, 5)
+    out["our_gemm_only_clocks"] = brief(clk)
     if world > 1:
         Dn = torch.empty(M // world, N, device=dev, dtype=torch.bfloat16)
         ms, _, _ = time_steps(torch, dist, world, lambda: impl.gemm_reducescatter_fused(A, B, Dn, algo), steps, warm, flush)
