@@ -448,6 +448,32 @@ def extras(torch, dist, impl, rank, world, dev, A, B, C, algo, flush, peaks, ste
     rs["cublas_nccl_rmsnorm_ms"] = round(msb, 5)
     rs["speedup_vs_cublas_nccl"] = round(msb / ms, 4)
     out["rs_rmsnorm"] = rs
+
+    # Where the fused step's time goes (several ranks only): the depth of the push pipeline, and
+    # the step with parts of the collective switched off (results are wrong in those runs; they
+    # come last and nothing reads C afterwards).
+    if world > 1:
+        study = {}
+        try:
+            cfg_a = config.default_solution(M, N, algo)
+            RA_a = layout.reorder_indices((M // cfg_a["BM"]) * (N // cfg_a["BN"]), cfg_a["hint"], device=dev)
+            mm_a = torch.zeros(1, max(N // cfg_a["BN"], 8), device=dev, dtype=torch.int32)
+            fused = lambda: impl.gemm_allreduce_overlap(A, B, C, mm_a, RA_a, 1, empty, empty_gpu, algo, False)
+            for lag in (1, 2, 4):
+                impl.set_option("push_lag", lag)
+                ms, _, _ = time_steps(torch, dist, world, fused, steps, warm, flush)
+                study[f"push_lag_{lag}_ms"] = round(ms, 5)
+            impl.set_option("push_lag", 0)
+            for bits, name in ((1, "no_reduction_traffic"), (2, "no_push_stores"), (3, "neither")):
+                impl.set_option("diag", bits)
+                ms, _, _ = time_steps(torch, dist, world, fused, steps, warm, flush)
+                study[f"{name}_ms"] = round(ms, 5)
+        except Exception as ex:
+            study["error"] = repr(ex)[:200]
+        finally:
+            impl.set_option("push_lag", 0)
+            impl.set_option("diag", 0)
+        out["fused_step_study"] = study
     impl.check_status()
     return out
 
