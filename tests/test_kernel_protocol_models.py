@@ -1,4 +1,4 @@
-"""CPU restatements of two pieces of in-kernel logic, checked against their specifications.
+"""CPU restatements of pieces of in-kernel logic, checked against their specifications.
 
 1. The hand-over of epilogue chunk buffers between the epilogue warps and the push warp of the
    fused kernels (csrc/gemm/fo_gemm_sm100.cuh): EPI buffers, one `ready` and one `free` mbarrier per
@@ -9,6 +9,10 @@
    that neither side gets stuck.
 2. The arithmetic of the RMSNorm tail of the reduce-scatter reducers: sum the partials in fp32,
    round, accumulate the squares of the ROUNDED values, then y = round(round(x * scale) * w).
+3. The cross-rank protocol of the fused collectives over several back-to-back calls - arrival
+   counters, `done` epochs, counter clearing by a rank's last CTA, staging reuse - for the push
+   and the pull protocol, under random interleavings of all ranks' CTAs.
+4. The `ready` / `done` handshakes that frame the fused GEMM + all-to-all.
 """
 import random
 
