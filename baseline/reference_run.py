@@ -11,7 +11,9 @@ Tuning inputs are produced in-process the way the reference's scripts produce th
      (tune/profile_config.py:85-93);
   2. hint: monitor-mode runs with the identity tile order; tiles whose completion rank falls into
      the same wave in all 10 samples form that wave; a candidate whose waves are not stable is
-     rejected (tune/search.py:111-157); rank 0's hint is used by every rank (:178);
+     rejected (tune/search.py:111-157); rank 0's hint is used by every rank (:178); when no
+     candidate is stable (its tuner then stops with "Tuning fails", :414) the tile order of one
+     monitor run is used instead - any permutation is a correct hint, only less well matched;
   3. cSeg: a handful of wave partitions (all-in-one = its non-overlapped path, halves, thirds,
      quarters, one wave per group) are timed and the fastest kept - a subset of its exhaustive
      search (tune/search.py:387-439), whose full 2**(waves-1) enumeration does not fit a benchmark.
@@ -101,6 +103,7 @@ def run(args, lib_path: str) -> None:
     else:
         # 2. hint by monitor runs, 3. wave partition by timing
         chosen = None
+        one_run = None  # (algo, ..., completion order of one monitor run): used when no stable order exists
         # wave window: one wave of (SMs - 2) tiles as in its exhaustive search, then the coarser
         # window of its predictive search (ceil(waves / 10) waves, tune/search.py:462-466)
         for coarse in (False, True):
@@ -124,6 +127,8 @@ def run(args, lib_path: str) -> None:
                     impl.gemm_allreduce_overlap(A, B, C, mm, ident, 1, cseg_cpu, cseg_gpu, algo, True)
                     samples[i] = mm[1:].reshape(-1)
                 torch.cuda.synchronize()
+                if one_run is None:
+                    one_run = (algo, BM, BN, tm, tn, tiles, wsize, waves, samples[-1].clone())
                 hint, ok = [], True
                 for w in range(waves):
                     idx = torch.where(((samples >= w * wsize) & (samples < (w + 1) * wsize)).sum(0) == 10)[0]
@@ -141,11 +146,26 @@ def run(args, lib_path: str) -> None:
                 break
             if chosen is not None:
                 break
+        if chosen is None and one_run is not None:
+            # Its tuner gives up here ("Tuning fails", tune/search.py:414).  To still give its overlap
+            # path a chance, take the tile order of ONE monitor run of its fastest GEMM as the hint:
+            # any permutation is a correct hint (groups are counted by membership, not by time), it
+            # is only less well matched to the real completion order.  The wave groupings below
+            # include its non-overlapped call, so the arm never gets slower by this.
+            try:
+                algo, BM, BN, tm, tn, tiles, wsize, waves, order = one_run
+                payload = [torch.argsort(order.long()).tolist() if rank == 0 else None]
+                dist.broadcast_object_list(payload, src=0)
+                if sorted(payload[0]) == list(range(tiles)):
+                    chosen = (algo, BM, BN, tm, tn, tiles, wsize, waves, payload[0])
+                    tuning["hint"] = "order of one monitor run (its stability check failed)"
+            except Exception as ex:
+                tuning["hint_error"] = repr(ex)[:200]
+                chosen = None
         if chosen is None:
-            # Its tuner gives up here ("Tuning fails", tune/search.py:414): no overlap config
-            # exists for this shape on this GPU.  What a user of the reference is left with is its
-            # non-overlapped call, which is also what its speed test runs for a single group
-            # (test/test.py:104-134).
+            # No overlap config exists for this shape on this GPU.  What a user of the reference is
+            # left with is its non-overlapped call, which is also what its speed test runs for a
+            # single group (test/test.py:104-134).
             algo = ranked[0]
             step = lambda a=None: impl.gemm_allreduce(A if a is None else a, B, C, algo)
             path = "OverlapImpl.gemm_allreduce (its tuner found no stable tile order: no overlap config)"
@@ -184,6 +204,8 @@ def run(args, lib_path: str) -> None:
         else:
             step = lambda a=None: impl.gemm_allreduce_overlap(A if a is None else a, B, C, mm, RA, 1, cc, cg, algo, False)
             path = "OverlapImpl.gemm_allreduce_overlap"
+            if "hint" in tuning:
+                path += " (hint: " + tuning["hint"] + ")"
 
     sampler = bench.ClockSampler(local) if rank == 0 else None
     ms, clocks, wall = bench.time_steps(torch, dist, world, step, args.steps, args.warmup, flush, sampler)
