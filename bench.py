@@ -34,7 +34,9 @@ M_RS, N_RS, K_RS_TOTAL = 16384, 8192, 8192
 # 7 % apart between an arm timed half a second after the first load and one timed seconds later,
 # while the board's power management was still settling under the 1 kW cap.
 WARM_SECONDS = 1.0
-NVLINK_GBS = 770.0           # measured peer-copy bandwidth per direction per GPU on this pool
+CHECK_ROWS_PER_PANEL = 8     # rows of every 128-row panel compared with the fp32 reference
+TIMED_BLOCKS = 5             # blocks of `steps` steps; the median block is the reported one
+NVLINK_GBS = 770.0           # measured peer-copy bandwidth per direction per GPU (B200, NVLink 5)
 REAL_STDOUT = sys.stdout
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
@@ -114,38 +116,44 @@ class ClockSampler:
         return out
 
 
-def pick_algo(torch, dist, world, run, candidates, reps=10, settle_seconds=0.5):
+def pick_algo(torch, dist, world, run, candidates, flush, reps=10, settle_seconds=WARM_SECONDS):
     """Fastest Algo by a short timing, agreed on by all ranks (max over ranks per candidate).
-    The candidates are ranked under load: a cold GPU runs all of them at boost clocks, while the
-    timed region runs at the power cap, where the kernels that move fewer bytes win."""
+    The candidates are ranked in the regime of the timed region: after the same settling time
+    under load (a cold GPU runs all of them at boost clocks, while the timed region runs at the
+    power cap, where the kernels that move fewer bytes win), with the L2 flushed between calls
+    and per-call events."""
     try:
         run(candidates[0])
         torch.cuda.synchronize()
         t0 = time.perf_counter()
         run(candidates[0])
+        flush()
         torch.cuda.synchronize()
         one = torch.tensor([max(time.perf_counter() - t0, 1e-5)], device="cuda")
         if world > 1:
             dist.all_reduce(one, op=dist.ReduceOp.MAX)       # same number of settling steps on every rank
-        for _ in range(int(min(1000, settle_seconds / one.item()))):
+        for _ in range(int(min(2000, settle_seconds / one.item()))):
             run(candidates[0])
+            flush()
     except Exception:
         pass
     times = []
     for a in candidates:
         try:
-            for _ in range(2):
+            for _ in range(3):
                 run(a)
-            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                flush()
+            ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(reps)]
             torch.cuda.synchronize()
             if world > 1:
                 dist.barrier()
-            s.record()
-            for _ in range(reps):
+            for s, e in ev:
+                flush()
+                s.record()
                 run(a)
-            e.record()
+                e.record()
             torch.cuda.synchronize()
-            times.append(s.elapsed_time(e) / reps)
+            times.append(sum(s.elapsed_time(e) for s, e in ev) / reps)
         except Exception:
             times.append(1e9)
     t = torch.tensor(times, device="cuda")
@@ -154,13 +162,10 @@ def pick_algo(torch, dist, world, run, candidates, reps=10, settle_seconds=0.5):
     return candidates[int(t.argmin().item())], [round(x, 4) for x in t.tolist()]
 
 
-def time_steps(torch, dist, world, fn, steps, warmup, flush, sampler=None):
-    """Per-step CUDA events on the launching stream, L2 flushed between steps (outside the
-    event pairs), barrier + synchronize on both sides.  Returns (mean ms over steps, max over
-    ranks), the clock record and the wall time of the bracket."""
-    # Warm up by count AND by time: the GPU settles at its power-capped clocks only after a few
-    # hundred milliseconds of load, and every arm must be measured in that state.  The number of
-    # extra warm-up steps is agreed on by all ranks so that everybody runs the same sequence.
+def _settle(torch, dist, world, fn, warmup, flush):
+    """Warm up by count AND by time: the GPU settles at its power-capped clocks only after a few
+    hundred milliseconds of load, and every arm must be measured in that state.  The number of
+    extra warm-up steps is agreed on by all ranks so that everybody runs the same sequence."""
     torch.cuda.synchronize()
     t_warm = time.perf_counter()
     for _ in range(warmup):
@@ -174,13 +179,17 @@ def time_steps(torch, dist, world, fn, steps, warmup, flush, sampler=None):
     for _ in range(extra_warm):
         fn()
         flush()
+
+
+def _timed_block(torch, dist, world, fn, steps, flush):
+    """`steps` steps with per-step CUDA events on the launching stream, L2 flushed between steps
+    (outside the event pairs), barrier + synchronize on both sides.  Returns (mean ms per step,
+    max over ranks; wall seconds of the bracket)."""
     ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize()
-    if sampler:
-        sampler.start()
     t0 = time.perf_counter()
     for s, e in ev:
         flush()
@@ -192,12 +201,44 @@ def time_steps(torch, dist, world, fn, steps, warmup, flush, sampler=None):
         dist.barrier()
     torch.cuda.synchronize()
     wall = time.perf_counter() - t0
-    clocks = sampler.stop() if sampler else None
     ms = sum(s.elapsed_time(e) for s, e in ev) / steps
     t = torch.tensor([ms], device="cuda")
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    return float(t.item()), clocks, wall
+    return float(t.item()), wall
+
+
+def time_steps(torch, dist, world, fn, steps, warmup, flush, sampler=None):
+    """One timed block after the warm-up.  Returns (ms per step, clock record, wall seconds)."""
+    _settle(torch, dist, world, fn, warmup, flush)
+    if sampler:
+        sampler.start()
+    ms, wall = _timed_block(torch, dist, world, fn, steps, flush)
+    clocks = sampler.stop() if sampler else None
+    return ms, clocks, wall
+
+
+def time_blocks(torch, dist, world, fn, steps, warmup, flush, sampler=None, blocks=TIMED_BLOCKS):
+    """The headline timing: after the warm-up, `blocks` back-to-back blocks of exactly `steps`
+    steps, each bracketed by barrier + synchronize; the MEDIAN block is the reported one (a
+    single block of tens of milliseconds moves by several per cent with the board's power
+    management).  Returns (ms per step of the median block, clock record over all blocks, wall
+    seconds of the median block, the sorted per-block values)."""
+    _settle(torch, dist, world, fn, warmup, flush)
+    if sampler:
+        sampler.start()
+    res = [_timed_block(torch, dist, world, fn, steps, flush) for _ in range(blocks)]
+    clocks = sampler.stop() if sampler else None
+    res.sort(key=lambda r: r[0])
+    ms, wall = res[len(res) // 2]
+    return ms, clocks, wall, [round(r[0], 5) for r in res]
+
+
+def config_dict(M, N, K, world):
+    """The benchmark configuration, identical for the product arm and the reference arm."""
+    return {"model": "row-parallel down-proj GEMM+AllReduce (Llama-3-70B MLP shape)",
+            "M": M, "N": N, "K_total": K_AR_TOTAL, "K_per_rank": K, "global_batch": M, "seq_len": None,
+            "parallelism": f"tp{world}", "l2": "256 MB buffer written between timed steps"}
 
 
 def e2e_pipeline(torch, dist, world, host_in, dev_bufs, step_on, result_slice, host_out, steps, warmup):
@@ -268,6 +309,18 @@ def run_ours(args):
     from flashoverlap_b200.parallel import symm
     C, uses_multicast = symm.alloc_allreduce_output(impl, (M, N), torch.bfloat16, multicast=not args.no_nvls)
 
+    # Pull protocol of the fused kernel: partial tiles stay in this rank's staging buffer and the
+    # owners fetch them, through the NVSwitch's in-switch reduction when the staging has a
+    # multicast mapping.  Both protocols are candidates of the probe below.
+    protocols = ["push"]
+    stage_mc = False
+    if world > 1 and args.protocol in ("auto", "pull"):
+        try:
+            _, stage_mc = symm.alloc_stage(impl, M, N, torch.bfloat16, multicast=not args.no_nvls)
+            protocols = ["pull"] if args.protocol == "pull" else ["push", "pull"]
+        except Exception:
+            protocols = ["push"]
+
     state = {}
 
     def prepare(algo):
@@ -283,31 +336,43 @@ def run_ours(args):
     empty = torch.empty(0, dtype=torch.int32)
     empty_gpu = torch.empty(0, dtype=torch.int32, device=dev)
 
-    def step_algo(algo, a=A):
+    def step_cand(cand, a=A):
+        algo, proto = cand
         cfg, RA, mm = prepare(algo)
+        if world > 1:
+            impl.set_option("stage_local", 1 if proto == "pull" else 0)
         # per-tile flags (empty cSeg): the finest wave grouping, which the fused kernel prefers
         impl.gemm_allreduce_overlap(a, B, C, mm, RA, 1, empty, empty_gpu, algo, False)
         return C
 
-    tuned_path = config.config_path(M, N, K, "b200")
-    if os.path.exists(tuned_path) and config.is_tuned(config.load_config(tuned_path)):
-        algo, algo_times = int(config.load_config(tuned_path)["Algo"]), None
+    tuned = config.load_tuned(M, N, K, tp=world, comm_op="all_reduce", mode="fused", gpu="b200")
+    if tuned is not None:
+        cand, algo_times, cands = (int(tuned["Algo"]), tuned.get("protocol", protocols[-1])), None, None
+        if cand[1] not in protocols:
+            cand = (cand[0], protocols[-1])
     else:
-        algo, algo_times = pick_algo(torch, dist, world, step_algo, [19, 3, 17, 1])
+        cands = [(a, pr) for pr in protocols for a in ((19, 3, 17, 1) if world <= 2 else (3, 1, 19, 17))]
+        cand, algo_times = pick_algo(torch, dist, world, step_cand, cands, flush)
+    algo, protocol = cand
 
     sampler = ClockSampler(local) if rank == 0 else None
-    ms, clocks, wall = time_steps(torch, dist, world, lambda: step_algo(algo), args.steps, args.warmup, flush, sampler)
+    ms, clocks, wall, blocks = time_blocks(torch, dist, world, lambda: step_cand(cand), args.steps, args.warmup, flush, sampler)
     impl.check_status()
     flops = 2.0 * M * N * K_AR_TOTAL
     value = flops / (ms * 1e-3) / 1e12
 
-    # correctness spot check of the timed path against torch (row block 0, fp32 reference)
+    # correctness check of the timed path against torch: CHECK_ROWS_PER_PANEL rows out of every
+    # 128-row panel, all columns, fp32 reference summed over the ranks
     cfg, RA, _ = prepare(algo)
     nat = ops.unreorder(C, M, N, cfg["BM"], cfg["BN"], RA)
-    ref = A[:128].float() @ B.float().t()
+    g = torch.Generator().manual_seed(7)
+    rows = torch.cat([p * 128 + torch.randperm(128, generator=g)[:CHECK_ROWS_PER_PANEL] for p in range(M // 128)]).to(dev)
+    ref = A[rows].float() @ B.float().t()
     if world > 1:
         dist.all_reduce(ref)
-    check_err = float((nat[:128].float() - ref).abs().max().item())
+    check_err = float((nat[rows].float() - ref).abs().max().item())
+    check_ref_max = float(ref.abs().max().item())
+    del nat, ref
 
     # ---- end to end: pinned host input every step, result slice read back every step
     host_in = torch.empty(M, K, dtype=torch.bfloat16).pin_memory()
@@ -315,10 +380,11 @@ def run_ours(args):
     host_out = torch.empty(128, N, dtype=torch.bfloat16).pin_memory()
     dev_bufs = [torch.empty_like(A), torch.empty_like(A)]
     e2e_steps = max(3, min(args.steps, 30))
-    e2e_ms = e2e_pipeline(torch, dist, world, host_in, dev_bufs, lambda a: step_algo(algo, a),
+    e2e_ms = e2e_pipeline(torch, dist, world, host_in, dev_bufs, lambda a: step_cand(cand, a),
                           lambda out: out.view(-1)[: 128 * N].view(128, N), host_out, e2e_steps,
                           max(3, min(args.warmup, 5)))
     impl.check_status()
+    del host_in, dev_bufs
 
     # ---- roofline of the fused step
     S = M * N * 2
@@ -326,13 +392,26 @@ def run_ours(args):
     t_link = (2.0 * S * (world - 1) / world) / (NVLINK_GBS * 1e9) if world > 1 else 0.0
     roof_ms = max(t_gemm, t_link) * 1e3
 
-    extra = {"algo": algo, "algo_probe_ms": algo_times, "allreduce_broadcast": "multimem.st (NVLS)" if uses_multicast else "peer stores", "check_max_abs_err": check_err,
+    how_reduced = "none (one rank)"
+    if world > 1:
+        how_reduced = ("pull: partials staged locally, owners sum them with multimem.ld_reduce (in-switch)" if stage_mc
+                       else "pull: partials staged locally, owners sum them with peer loads") if protocol == "pull" \
+            else "push: partials stored into the owners' staging with TMA, summed by the owners' reducer warps"
+    extra = {"algo": algo, "protocol": protocol, "reduction": how_reduced,
+             "probe_candidates": [list(c) for c in cands] if cands else None, "probe_ms": algo_times,
+             "allreduce_broadcast": "multimem.st (NVLS)" if uses_multicast else "peer stores",
+             "check_max_abs_err": check_err, "check_ref_max_abs": check_ref_max, "check_rows": int(rows.numel()),
+             "ms_per_step_blocks": blocks,
+             "timing": f"{TIMED_BLOCKS} blocks of `steps` steps (per-step CUDA events on the launching stream, mean over "
+                       "the block, max over ranks); ms_per_step is the median block",
              "roofline_ms": round(roof_ms, 4), "roofline_frac": round(roof_ms / ms, 4),
              "roofline_peaks": peaks["source"], "wall_s_timed_region": round(wall, 3)}
 
     if not args.no_extra:
         try:
-            extra.update(extras(torch, dist, impl, rank, world, dev, A, B, C, algo, flush, peaks, args.steps))
+            extra.update(extras(torch, dist, impl, rank, world, dev, A, B, C, algo, flush, peaks, args.steps, protocol,
+                                protocols, args.no_nvls))
+            extra.update(reference_ratios(world, ms, extra))
         except Exception as ex:  # extras never block the headline line
             extra["extras_error"] = repr(ex)[:300]
 
@@ -341,15 +420,13 @@ def run_ours(args):
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 5),
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic", "impl": "ours",
-        "config": {"model": "row-parallel down-proj GEMM+AllReduce (Llama-3-70B MLP shape)",
-                   "M": M, "N": N, "K_total": K_AR_TOTAL, "K_per_rank": K, "global_batch": M, "seq_len": None,
-                   "parallelism": f"tp{world}", "l2": "256 MB buffer written between timed steps",
-                   "timing": "per-step CUDA events on the launching stream, mean over steps, max over ranks"},
+        "config": config_dict(M, N, K, world),
         "clocks": clocks,
         "e2e": {"value": round(flops / (e2e_ms * 1e-3) / 1e12, 2), "unit": "TFLOP/s", "ms_per_step": round(e2e_ms, 5),
                 "steps": e2e_steps, "h2d_bytes_per_step": M * K * 2, "d2h_bytes_per_step": 128 * N * 2,
                 "note": "input copied from pinned host memory every step (double-buffered, overlapping "
-                        "the previous step's kernel); first 128 result rows read back every step"},
+                        "the previous step's kernel); the first 128 of the 8192 result rows (1.6 % of the result) "
+                        "are read back every step"},
         "gpu_launches": args.steps * 1,
         "extra": extra,
     }
@@ -360,7 +437,8 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
-def extras(torch, dist, impl, rank, world, dev, A, B, C, algo, flush, peaks, steps_main):
+def extras(torch, dist, impl, rank, world, dev, A, B, C, algo, flush, peaks, steps_main, protocol="push",
+           protocols=("push",), no_nvls=False):
     """Comparison arms on the same box: our GEMM then one NCCL call (non-overlap), cuBLAS + NCCL,
     the counter-gated NCCL mechanism, and the GEMM+ReduceScatter+RMSNorm config."""
     from flashoverlap_b200 import ops
@@ -414,30 +492,58 @@ def extras(torch, dist, impl, rank, world, dev, A, B, C, algo, flush, peaks, ste
         finally:
             impl.set_option("mode", 0)
 
-    # GEMM + ReduceScatter + RMSNorm (sequence-parallel o_proj shape)
+    # GEMM + ReduceScatter + RMSNorm (sequence-parallel o_proj shape).  Candidates: the fused
+    # reduce-scatter (push or pull protocol) into the tile-contiguous shard followed by the fused
+    # un-reorder+RMSNorm kernel, and the fused reduce-scatter whose reducers normalise each row
+    # panel themselves (RMSNorm tail, push protocol); the fastest in a short probe is timed.
+    from flashoverlap_b200.parallel import symm
     M2, N2, K2 = M_RS, N_RS, K_RS_TOTAL // world
     A2 = (torch.randn(M2, K2, device=dev) * 0.02).to(torch.bfloat16)
     B2 = (torch.randn(N2, K2, device=dev) * 0.02).to(torch.bfloat16)
     w = (1 + 0.02 * torch.randn(N2, device=dev)).to(torch.bfloat16)
     D = torch.empty(M2 // world, N2, device=dev, dtype=torch.bfloat16)
     Y = torch.empty_like(D)
-    cfg = config.default_solution(M2, N2, algo)
-    tiles = (M2 // cfg["BM"]) * (N2 // cfg["BN"])
-    RA = layout.reorder_indices(tiles, cfg["hint"], device=dev)
-    mm = torch.zeros(1, N2 // cfg["BN"], device=dev, dtype=torch.int32)
     empty, empty_gpu = torch.empty(0, dtype=torch.int32), torch.empty(0, dtype=torch.int32, device=dev)
-    bm_local = cfg["BM"] // world
+    rs_protocols = ["push"]
+    if world > 1 and "pull" in protocols:
+        try:
+            symm.alloc_stage(impl, M2, N2, torch.bfloat16, multicast=not no_nvls)
+            rs_protocols.append("pull")
+        except Exception:
+            pass
+    rs_state = {}
 
-    def rs_step():
-        impl.gemm_reducescatter_overlap(A2, B2, D, D, mm, RA, empty_gpu, 1, empty, empty_gpu, algo, False)
-        torch.ops.flashoverlap_op.reorder_rmsnorm_eps(D, Y, w, bm_local, cfg["BN"], 1, RA, 1e-5)
+    def rs_step(cand):
+        a, proto, how = cand
+        if a not in rs_state:
+            c2 = config.default_solution(M2, N2, a)
+            t2 = (M2 // c2["BM"]) * (N2 // c2["BN"])
+            rs_state[a] = (c2, layout.reorder_indices(t2, c2["hint"], device=dev),
+                           torch.zeros(1, N2 // c2["BN"], device=dev, dtype=torch.int32))
+        c2, RA2, mm2 = rs_state[a]
+        if world > 1:
+            impl.set_option("stage_local", 1 if proto == "pull" else 0)
+        if how == "tail":
+            impl.gemm_reducescatter_rmsnorm_fused(A2, B2, Y, w, 1e-5, a)
+        else:
+            impl.gemm_reducescatter_overlap(A2, B2, D, D, mm2, RA2, empty_gpu, 1, empty, empty_gpu, a, False)
+            torch.ops.flashoverlap_op.reorder_rmsnorm_eps(D, Y, w, c2["BM"] // world, c2["BN"], 1, RA2, 1e-5)
 
-    ms, _, _ = time_steps(torch, dist, world, rs_step, steps, warm, flush)
+    rs_cands = [(a, pr, "norm_kernel") for pr in rs_protocols for a in (0, 1, 3)]
+    if world > 1:
+        rs_cands += [(a, "push", "tail") for a in (0, 1)]
+    rs_cand, rs_probe = pick_algo(torch, dist, world, rs_step, rs_cands, flush, settle_seconds=0.3)
+    ms, _, _ = time_steps(torch, dist, world, lambda: rs_step(rs_cand), steps, warm, flush)
+    if world > 1:
+        impl.set_option("stage_local", 1 if protocol == "pull" else 0)
     S2 = M2 * N2 * 2
     t_gemm = 2.0 * M2 * N2 * K2 / (peaks["bf16_tflops"] * 1e12)
     t_link = (S2 * (world - 1) / world) / (NVLINK_GBS * 1e9) if world > 1 else 0.0
     t_norm = 2.0 * (S2 / world) / (peaks["hbm_gbs"] * 1e9)
-    rs = {"ms": round(ms, 5), "roofline_ms": round((max(t_gemm, t_link) + t_norm) * 1e3, 4), "M": M2, "N": N2, "K_per_rank": K2}
+    rs = {"ms": round(ms, 5), "roofline_ms": round((max(t_gemm, t_link) + t_norm) * 1e3, 4), "M": M2, "N": N2, "K_per_rank": K2,
+          "algo": rs_cand[0], "protocol": rs_cand[1], "rmsnorm": rs_cand[2],
+          "probe": {f"{a}/{pr}/{how}": t for (a, pr, how), t in zip(rs_cands, rs_probe)}}
+    rs["roofline_frac"] = round(rs["roofline_ms"] / ms, 4)
     C2 = torch.empty(M2, N2, device=dev, dtype=torch.bfloat16)
 
     def rs_base():
@@ -478,6 +584,32 @@ def extras(torch, dist, impl, rank, world, dev, A, B, C, algo, flush, peaks, ste
     return out
 
 
+def reference_ratios(world, ms, extra):
+    """Ratios against the reference arm's last run at this world size, when that arm has run on
+    this machine (it leaves its JSON line in the git-ignored baseline/_ref)."""
+    try:
+        from baseline import reference_run
+        with open(reference_run.last_run_path(world)) as f:
+            ref = json.load(f)
+    except Exception:
+        return {}
+    rx = ref.get("extra", {})
+    out = {"reference_ms_per_step": ref.get("ms_per_step"), "reference_path": rx.get("path")}
+    if ref.get("ms_per_step"):
+        out["speedup_vs_reference_overlap"] = round(ref["ms_per_step"] / ms, 4)
+    if rx.get("baseline_impl_ms"):
+        out["reference_baseline_impl_ms"] = rx["baseline_impl_ms"]
+        out["speedup_vs_reference_baseline_impl"] = round(rx["baseline_impl_ms"] / ms, 4)
+    rs = extra.get("rs_rmsnorm")
+    if rs and rx.get("rs_rmsnorm_ms"):
+        rs["reference_rs_rmsnorm_ms"] = rx["rs_rmsnorm_ms"]
+        rs["speedup_vs_reference"] = round(rx["rs_rmsnorm_ms"] / rs["ms"], 4)
+    if rs and rx.get("rs_baseline_impl_ms"):
+        rs["reference_rs_baseline_impl_ms"] = rx["rs_baseline_impl_ms"]
+        rs["speedup_vs_reference_baseline_impl"] = round(rx["rs_baseline_impl_ms"] / rs["ms"], 4)
+    return out
+
+
 def run_reference(args):
     from baseline import reference_arm
     reference_arm.main(args)
@@ -502,7 +634,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-extra", action="store_true", help="skip the comparison arms")
-    ap.add_argument("--no-nvls", action="store_true", help="broadcast all-reduce results with peer stores only")
+    ap.add_argument("--no-nvls", action="store_true", help="no NVSwitch multicast: peer stores / peer loads only")
+    ap.add_argument("--protocol", choices=["auto", "push", "pull"], default="auto",
+                    help="fused-collective protocol; auto = the faster of the two in a short probe")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3

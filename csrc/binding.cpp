@@ -196,7 +196,9 @@ TORCH_LIBRARY(flashoverlap_class, m) {
       .def("set_trace", &OverlapImpl::SetTrace)
       .def("read_status", &OverlapImpl::ReadStatus)
       .def("check_status", &OverlapImpl::CheckStatus)
-      .def("reset_status", &OverlapImpl::ResetStatus);
+      .def("reset_status", &OverlapImpl::ResetStatus)
+      .def("resync", &OverlapImpl::Resync)
+      .def("wait_flag", &OverlapImpl::WaitFlag);
 }
 
 TORCH_LIBRARY(flashoverlap_op, m) {

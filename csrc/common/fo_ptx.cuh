@@ -80,6 +80,22 @@ FO_DEVICE bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
+// The same test with an explicit limit on how long the hardware may keep the thread suspended
+// before it returns unsatisfied (it still resumes at once when the phase completes).
+FO_DEVICE bool mbar_try_wait_suspend(uint64_t* bar, uint32_t parity, uint32_t suspend_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred P;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, P;\n\t"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(suspend_ns)
+      : "memory");
+  return ok != 0;
+}
+
 // Time base of the bounded waits: the SM cycle counter.  Reading %globaltimer costs on the
 // order of a microsecond, which is ruinous inside a hand-off between warps that happens several
 // times per tile; clock64 costs a few cycles.  Timeouts given in nanoseconds are converted
@@ -102,21 +118,25 @@ FO_DEVICE uint64_t ns_to_cycles(uint64_t ns) { return ns * 2ull; }
 
 // Bounded mbarrier wait.  `abort_flag` is a CTA-shared word any role sets when it gives
 // up, so the other roles leave their own waits promptly instead of each running to
-// its limit.  try_wait itself suspends the thread for a short, implementation-defined time;
-// the abort flag and the cycle budget are looked at every 32 polls only.  Returns false on
-// timeout or abort.
+// its limit.  After 32 quick polls the thread lets the hardware suspend it for up to
+// kMbarSuspendNs per poll; the abort flag and the cycle budget are looked at every 8 of those.
+// Returns false on timeout or abort.
 constexpr uint32_t kMbarDrainPolls = 1u << 20;  // poll bound used only while draining at exit
+constexpr uint32_t kMbarSuspendNs = 4000;       // longest hardware suspension of one slow-path poll
 
 FO_DEVICE bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                  uint64_t timeout_ns) {
   for (uint32_t it = 0; it < 32u; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
   }
+  // A wait that has not been satisfied by now is a long one (a role that runs ahead of the
+  // pipeline, or an idle epilogue during a main loop): let the hardware park the thread for up
+  // to kMbarSuspendNs per poll instead of spinning through the issue slots of a busy SM.
   const uint64_t t0 = cycles_now();
   const uint64_t budget = ns_to_cycles(timeout_ns);
   for (uint32_t it = 1;; ++it) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((it & 31u) == 0u) {
+    if (mbar_try_wait_suspend(bar, parity, kMbarSuspendNs)) return true;
+    if ((it & 7u) == 0u) {
       if (*abort_flag) return false;
       if (cycles_now() - t0 > budget) return false;
     }

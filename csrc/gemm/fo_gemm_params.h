@@ -36,7 +36,8 @@ struct GemmTensorMaps {
   CUtensorMap b[kMaxVirtualRanks];
   // fused kernels: every rank's staging buffer viewed as [ws * tiles * rows_owned, BN], box
   // (rows_owned x 64): the epilogue's pushes are TMA stores through these.  Pull variant: this
-  // rank's own staging viewed as [tiles * 128, BN], box (128 x 64).
+  // rank's own staging viewed as [tiles * 128, BN], box (128 x 64).  Plain kernels: st[virtual
+  // rank] is the output map of that rank (GemmParams::tma_out), box (128 x 64).
   CUtensorMap st[kMaxRanks];
 };
 
@@ -103,6 +104,10 @@ struct GemmParams {
   // Fused kernels: 4 selects the build with four epilogue chunk buffers (and one operand stage
   // fewer), whose push warp keeps three chunks of stores in flight; anything else the default (2).
   int epi_bufs;
+  // Plain kernels: 1 = GemmTensorMaps::st[virtual rank] describes the output as a 2-D tensor
+  // (row-major [M, N], or the tile-contiguous layout as [M * N / (rldn * BN), rldn * BN]) and
+  // finished chunks leave shared memory as TMA tensor stores; 0 = per-thread 16-byte stores.
+  int tma_out;
 };
 
 constexpr int kTraceSlots = 8;

@@ -117,6 +117,20 @@ __device__ __forceinline__ void group_of_position(const GemmParams& p, int r, in
   *need = n;
 }
 
+// Reordered position of natural tile t.  A value outside [0, tiles) - a corrupted RA, or one
+// built for another shape - would become an out-of-range address and counter index: it is
+// reported (kStatusBadArgument) and replaced by t, so the kernel stays inside its buffers;
+// the result is then wrong and the status words say why.
+__device__ __forceinline__ int tile_position(const GemmParams& p, int t, int32_t* status) {
+  if (p.RA == nullptr) return t;
+  const int r = p.RA[t];
+  if (static_cast<unsigned>(r) >= static_cast<unsigned>(p.num_tiles)) {
+    ptx::report_status(status, kStatusBadArgument, 1, t, r);
+    return t;
+  }
+  return r;
+}
+
 constexpr int kEpilogueThreads = 128;
 constexpr int kReducerThreads = 128;
 constexpr int kThreadsPlain = 64 + kEpilogueThreads;
@@ -623,20 +637,25 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
           const uint32_t sa = ptx::smem_u32(smem + stage * L::kStageBytes);
           const uint64_t da = ptx::make_smem_desc_sw128_kmajor(sa);
           const uint64_t db = ptx::make_smem_desc_sw128_kmajor(sa + L::kABytes);
+          // advance 16 elements (32 B) along K inside the swizzle atom: +2 in 16-byte units
+          if constexpr (CTA2) {
 #pragma unroll
-          for (int k = 0; k < kBK / 16; ++k) {
-            // advance 16 elements (32 B) along K inside the swizzle atom: +2 in 16-byte units
-            if constexpr (CTA2) {
+            for (int h = 0; h < MT; ++h) {
+              // half h: its A rows sit h * 16 KB further in the stage, its accumulator BN
+              // columns further in TMEM; both halves multiply the same B tile.  The four MMAs
+              // of a half are issued back to back so that consecutive instructions accumulate
+              // into the same TMEM columns.
 #pragma unroll
-              for (int h = 0; h < MT; ++h) {
-                // half h: its A rows sit h * 16 KB further in the stage, its accumulator BN
-                // columns further in TMEM; both halves multiply the same B tile
+              for (int k = 0; k < kBK / 16; ++k) {
                 ptx::umma_f16_ss_pair(tmem_d + static_cast<uint32_t>(h * BN),
                                       da + static_cast<uint64_t>(h * (L::kAHalfBytes >> 4) + 2 * k),
                                       db + static_cast<uint64_t>(2 * k), idesc,
                                       (kb > 0 || k > 0) ? 1u : 0u);
               }
-            } else {
+            }
+          } else {
+#pragma unroll
+            for (int k = 0; k < kBK / 16; ++k) {
               ptx::umma_f16_ss(tmem_d, da + static_cast<uint64_t>(2 * k),
                                db + static_cast<uint64_t>(2 * k), idesc,
                                (kb > 0 || k > 0) ? 1u : 0u);
@@ -690,6 +709,12 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
     const uint32_t tmem_empty_addr0 =
         CTA2 ? ptx::mapa_shared(ptx::smem_u32(&tmem_empty_bar[0]), 0u) : ptx::smem_u32(&tmem_empty_bar[0]);
 
+    // Plain kernels store finished chunks with TMA (one tensor store per 128 x 64 chunk through
+    // the output map in maps.st[vr]) when the host could describe the output as a 2-D tensor
+    // (row-major and tile-contiguous layouts); the row-scatter and all-to-all modes, whose rows
+    // go to unrelated addresses, keep the per-thread 16-byte stores.
+    const bool use_tma = !FUSED && !A2A && p.tma_out != 0;
+
     bool go = true;
     if constexpr (A2A) {
       // Start-of-call handshake of the all-to-all: a rank's receive buffer may be overwritten
@@ -734,7 +759,7 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
       TileCoord tc = tc0;
       tc.m += h;
       const int t = tc.m * p.tiles_n + tc.n;
-      const int r = (p.RA != nullptr) ? p.RA[t] : t;
+      const int r = tile_position(p, t, status);
       if constexpr (TRACE) {
         if (et == 0) {
           stamp(t, kTraceAccReady);
@@ -747,8 +772,19 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
       // 16-byte piece (et & 7) of rows (et >> 3) + 16 * i, i = 0..7.
       uint8_t* row_ptr[8];
       uint32_t row_valid = 0xffu;  // all-to-all: bit i clear = row i has no destination
+      // TMA stores: coordinates of the tile's first chunk in the output's 2-D view
+      int tma_x0 = 0, tma_y0 = 0;
+      if (use_tma) {
+        if (p.out_mode == kOutNatural) {
+          tma_x0 = tc.n * BN;
+          tma_y0 = tc.m * kBM;
+        } else {  // tile-contiguous: [M * N / (rldn * BN)] rows of rldn * BN elements
+          tma_x0 = (r % p.rldn) * BN;
+          tma_y0 = (r / p.rldn) * kBM;
+        }
+      }
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
+      for (int i = 0; i < 8 && !use_tma; ++i) {
         const int lr = (et >> 3) + 16 * i;
         size_t off = 0;  // element offset of (row lr, tile column 0)
         uint8_t* base = nullptr;
@@ -780,7 +816,14 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
                   static_cast<size_t>(lr) * ld;
           } else {  // kOutScatterRows: rows of the [M*N/BN, BN] view are remapped through RE
             const size_t row_id = static_cast<size_t>(r) * kBM + lr;
-            off = static_cast<size_t>(p.RE[row_id]) * BN;
+            const int re = p.RE[row_id];
+            if (static_cast<unsigned>(re) >= static_cast<unsigned>(p.M) * static_cast<unsigned>(p.tiles_n)) {
+              // a row index outside the buffer: report it and drop the row
+              ptx::report_status(status, kStatusBadArgument, 2, static_cast<int32_t>(row_id), re);
+              row_valid &= ~(1u << i);
+            } else {
+              off = static_cast<size_t>(re) * BN;
+            }
           }
         }
         row_ptr[i] = base + off * elem + (et & 7) * 16;
@@ -809,6 +852,13 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
             *s_abort = 1;
           }
         }
+        if constexpr (!FUSED && !A2A) {
+          if (use_tma) {
+            // The store issued from this buffer two chunks ago must have read it.
+            if (et == 0) ptx::bulk_wait_group_read<1>();
+            ptx::named_bar_sync(1, kEpilogueThreads);
+          }
+        }
         const int bsel = FUSED ? static_cast<int>(chunk_no % EPI) : (c & 1);
         uint8_t* buf = epi + bsel * L::kEpiBufBytes + smem_row * 128;
         const int sw = smem_row & 7;
@@ -835,6 +885,13 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
           ptx::fence_proxy_async_smem();
           ptx::mbar_arrive(&chunk_ready_bar[chunk_no % EPI]);
           ++chunk_no;
+        } else if (use_tma) {
+          ptx::fence_proxy_async_smem();  // generic-proxy writes before the async-proxy read
+          ptx::named_bar_sync(1, kEpilogueThreads);
+          if (et == 0) {
+            ptx::tma_store_2d(&maps.st[vr], epi + (c & 1) * L::kEpiBufBytes, tma_x0 + c * 64, tma_y0);
+            ptx::bulk_commit_group();
+          }
         } else {
           ptx::named_bar_sync(1, kEpilogueThreads);
           const uint8_t* rbuf = epi + (c & 1) * L::kEpiBufBytes;
@@ -843,7 +900,7 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
             const int lr = (et >> 3) + 16 * i;
             const uint4 w =
                 *reinterpret_cast<const uint4*>(rbuf + lr * 128 + (((et & 7) ^ (lr & 7)) * 16));
-            if (!A2A || ((row_valid >> i) & 1u)) ptx::st_v4(row_ptr[i] + c * 128, w);
+            if ((row_valid >> i) & 1u) ptx::st_v4(row_ptr[i] + c * 128, w);
           }
         }
       }
@@ -853,9 +910,14 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
         if (et == 0) stamp(t, kTraceEpilogueDone);
       } else {
         // All of this tile's stores have been issued by every epilogue thread.
-        ptx::named_bar_sync(1, kEpilogueThreads);
+        if (!use_tma) ptx::named_bar_sync(1, kEpilogueThreads);
         if (et == 0 && p.MM[vr] != nullptr) {
           int* mm = p.MM[vr];
+          if (use_tma && (p.signal || p.monitor)) {
+            // The tile may be announced only once its tensor stores have been written.
+            ptx::bulk_wait_group<0>();
+            ptx::fence_proxy_async_all();
+          }
           if (p.signal) {
             int g, need;
             group_of_position(p, r, &g, &need);
@@ -879,6 +941,8 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
         acc_phase ^= 1u;
       }
     }
+    // No tensor store may still read this CTA's shared memory when the CTA exits.
+    if (use_tma && et == 0) ptx::bulk_wait_group<0>();
     if constexpr (A2A) {
       // End-of-call handshake of the all-to-all: once every CTA of this rank has issued its
       // stores, the last one tells every rank that this rank's rows have been sent and waits
@@ -916,7 +980,7 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
           pos += num_units;
         }
         const int t = tc.m * p.tiles_n + tc.n;
-        const int r = (p.RA != nullptr) ? p.RA[t] : t;
+        const int r = tile_position(p, t, status);
         if (rt == 0) {
           int g, need;
           group_of_position(p, r, &g, &need);
@@ -1077,7 +1141,7 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
             pos += num_units;
           }
           const int t = tc.m * p.tiles_n + tc.n;
-          const int r = (p.RA != nullptr) ? p.RA[t] : t;
+          const int r = tile_position(p, t, status);
           const int row0 = (me * p.num_tiles + t) * rows_owned;
           for (int c = 0; c < kChunks; ++c, ++chunk_no) {
             const int b = static_cast<int>(chunk_no % EPI);

@@ -42,7 +42,8 @@ extern "C" int fo_fused_loopback_noalloc(int comm_op, int ranks, const void* con
     return fail(-1, err, err_len, "ranks must be 2 or 4");
   if (A == nullptr || B == nullptr || out == nullptr) return fail(-1, err, err_len, "null pointer table");
   if (algo < 0 || algo >= kNumAlgos || algo_config(algo).cta2)
-    return fail(-1, err, err_len, "algo must be a single-CTA Algo index (Algo & 3 != 1)");
+    return fail(-1, err, err_len, "algo must be a single-CTA Algo index ((Algo & 1) == 0)");
+  if (M <= 0 || N <= 0 || K <= 0) return fail(-1, err, err_len, "M, N and K must be positive");
 
   GemmParams p;
   std::memset(&p, 0, sizeof(p));

@@ -97,6 +97,30 @@ inline void setup_stage_map(GemmTensorMaps* maps, int rank, void* stage, const G
   FO_CHECK(e.empty(), "staging map: ", e);
 }
 
+// Output map of a plain kernel for virtual rank `vr`: the row-major [M, N] output, or the
+// tile-contiguous layout viewed as [M * N / (rldn * BN), rldn * BN], box 128 x 64.  Sets
+// p->tma_out when the layout can be described that way; otherwise the kernel keeps its
+// per-thread stores (row-scatter and all-to-all outputs, a tile count that rldn does not divide,
+// an output whose address is not 16-byte aligned).
+inline void setup_out_map(GemmTensorMaps* maps, int vr, void* out, GemmParams* p, int bn) {
+  if (vr == 0) p->tma_out = 0;
+  uint64_t cols = 0;
+  if (p->out_mode == kOutNatural) {
+    cols = static_cast<uint64_t>(p->N);
+  } else if (p->out_mode == kOutReorder && p->rldn >= 1 && p->num_tiles % p->rldn == 0) {
+    cols = static_cast<uint64_t>(p->rldn) * bn;
+  } else {
+    return;
+  }
+  const uint64_t rows = static_cast<uint64_t>(p->M) * p->N / cols;
+  const std::string e = encode_tmap_16bit(&maps->st[vr], out, rows, cols, kBM);
+  if (e.empty()) {
+    if (vr == 0) p->tma_out = 1;
+  } else {
+    p->tma_out = 0;
+  }
+}
+
 // Send/receive plan of the variable-size all-to-all on packed rows for rank `me`
 // (reference semantics, src/overlap_impl.cu:181-212): mlen is the row-major [ws, ws] matrix of
 // row counts, rank r sends mlen[r][i] rows to rank i, the runs for the other ranks are packed in

@@ -102,6 +102,11 @@ void OverlapImpl::SetOption(std::string name, int64_t value) {
   } else if (name == "diag") {
     FO_CHECK(value >= 0 && value <= 7, "diag is a bit mask of 1 | 2 | 4");
     opt_diag_ = value;
+  } else if (name == "validate") {
+    opt_validate_ = value ? 1 : 0;
+  } else if (name == "tma_out") {
+    FO_CHECK(value >= -1 && value <= 1, "tma_out must be -1 (automatic), 0 or 1");
+    opt_tma_out_ = value;
   } else if (name == "epi_bufs") {
     FO_CHECK(value == 2 || value == 4, "epi_bufs must be 2 or 4");
     opt_epi_bufs_ = value;
@@ -120,6 +125,8 @@ int64_t OverlapImpl::GetOption(std::string name) {
   if (name == "push_lag") return opt_push_lag_;
   if (name == "stage_local") return opt_stage_local_;
   if (name == "epi_bufs") return opt_epi_bufs_;
+  if (name == "tma_out") return opt_tma_out_;
+  if (name == "validate") return opt_validate_;
   if (name == "diag") return opt_diag_;
   if (name == "sm_count") return sm_count_;
   if (name == "rank") return rank_;
@@ -213,6 +220,45 @@ void OverlapImpl::ResetStatus() {
   }
 }
 
+void OverlapImpl::WaitFlag(int64_t target, at::Tensor MM, int64_t index) {
+  // The bounded counting wait of the gated path as a call of its own, on the caller's stream
+  // (reference: kernel_wait_flag, src/wait.cuh:5-9, which spins without a limit).  Gives up
+  // after "timeout_ms" and records that in this object's status words.
+  FO_CHECK(status_.defined(), "call nccl_init first");
+  FO_CHECK(MM.is_cuda() && MM.scalar_type() == at::kInt && MM.is_contiguous(), "MM must be a contiguous int32 CUDA tensor");
+  FO_CHECK(index >= 0 && index < MM.numel(), "counter index ", index, " outside MM (", MM.numel(), " entries)");
+  FO_CHECK(target > 0, "target must be positive");
+  cuda_check(wait_flag_launch(static_cast<int>(target), MM.data_ptr<int>() + index, static_cast<int>(index),
+                              static_cast<uint64_t>(opt_timeout_ms_) * 1000000ull, status_.data_ptr<int>(), stream()),
+             "wait kernel launch");
+}
+
+void OverlapImpl::Resync() {
+  // Collective re-alignment after a failed or skipped fused call.  A rank that missed a call
+  // (or gave up in one) disagrees with its peers about the call number and the `done` counters,
+  // and every later fused call would time out.  All ranks: finish what is in flight, agree that
+  // everybody has stopped (first barrier), clear the local counters, agree that everybody has
+  // cleared (second barrier), restart the call numbering.
+  FO_CHECK(heap_ != nullptr, "call nccl_init first");
+  cudaStream_t s = stream();
+  cuda_check(cudaStreamSynchronize(s), "cudaStreamSynchronize");
+  at::Tensor token = at::zeros({1}, at::TensorOptions().dtype(at::kFloat).device(at::kCUDA, device_));
+  auto barrier = [&]() {
+    if (world_ > 1) {
+      FO_NCCL_CHECK(ncclAllReduce(token.data_ptr(), token.data_ptr(), 1, ncclFloat32, ncclSum, comm_, s));
+    }
+    cuda_check(cudaStreamSynchronize(s), "cudaStreamSynchronize");
+  };
+  barrier();
+  if (signal_ != nullptr) cuda_check(cudaMemsetAsync(signal_->local(), 0, kSignalBytes, s), "cudaMemsetAsync");
+  status_.zero_();
+  if (norm_ssq_.defined()) norm_ssq_.zero_();
+  if (norm_cnt_.defined()) norm_cnt_.zero_();
+  barrier();
+  epoch_ = 0;
+  a2a_epoch_ = 0;
+}
+
 // ---------------------------------------------------------------------------- plain GEMM
 
 void OverlapImpl::run_plain(const at::Tensor& A, const at::Tensor& B, void* out, int out_mode,
@@ -243,6 +289,11 @@ void OverlapImpl::run_plain(const at::Tensor& A, const at::Tensor& B, void* out,
   p.out[0] = out;
   p.MM[0] = MM;
   p.status[0] = status_.data_ptr<int>();
+  // TMA tensor stores pay where the epilogue runs under the next tile's main loop; the kernels
+  // whose two accumulators fill TMEM (mt == 2) expose their epilogue and are faster with the
+  // fire-and-forget per-thread stores (measured: 4-15 % of the step at K per rank <= 28672).
+  const bool tma_out = opt_tma_out_ > 0 || (opt_tma_out_ < 0 && algo_config(algo).mt == 1);
+  if (tma_out) setup_out_map(&maps, 0, out, &p, algo_config(algo).bn);
   const int resident = gemm_max_resident_ctas(algo, bf16, false);
   const int grid = std::max(1, std::min(std::min(grid_cap, resident), p.num_tiles));
   cuda_check(launch_gemm(algo, bf16, false, maps, p, grid, 1, false, stream()), "GEMM launch");
@@ -412,7 +463,10 @@ void OverlapImpl::run_fused(int comm, const at::Tensor& A, const at::Tensor& B, 
     p.dst[rank_] = out.data_ptr();
   }
 
-  ++epoch_;
+  // The call number enters the kernel's handshakes; it is advanced only once nothing can
+  // reject the call any more (directly before the launch, and taken back if the launch fails):
+  // a call that throws must leave the object in step with its peers.
+  const uint32_t epoch = epoch_ + 1;
   set_l2_hints(&p, opt_l2_hints_ != 0);
   p.out_mode = out_mode;
   p.rldn = rldn < 1 ? 1 : rldn;
@@ -424,8 +478,8 @@ void OverlapImpl::run_fused(int comm, const at::Tensor& A, const at::Tensor& B, 
   p.rank_base = rank_;
   p.strided_rows = static_cast<int>(opt_strided_rows_);
   p.push_lag = opt_push_lag_ > 0 ? static_cast<int>(opt_push_lag_) : default_push_lag(p.K);
-  p.epoch_done_prev = static_cast<uint32_t>(world_) * (epoch_ - 1);
-  p.epoch_done = static_cast<uint32_t>(world_) * epoch_;
+  p.epoch_done_prev = static_cast<uint32_t>(world_) * (epoch - 1);
+  p.epoch_done = static_cast<uint32_t>(world_) * epoch;
   p.timeout_ns = static_cast<uint64_t>(opt_timeout_ms_) * 1000000ull;
   p.RA = RA;
   p.cseg = cseg;
@@ -467,7 +521,10 @@ void OverlapImpl::run_fused(int comm, const at::Tensor& A, const at::Tensor& B, 
     p.done[r] = reinterpret_cast<uint32_t*>(sig + kSignalDoneOffset);
   }
   const int grid = std::max(1, std::min(gemm_max_resident_ctas(algo, bf16, true), p.num_tiles));
-  cuda_check(launch_gemm(algo, bf16, true, maps, p, grid, 1, false, stream()), "fused GEMM launch");
+  epoch_ = epoch;
+  const cudaError_t launched = launch_gemm(algo, bf16, true, maps, p, grid, 1, false, stream());
+  if (launched != cudaSuccess) epoch_ = epoch - 1;
+  cuda_check(launched, "fused GEMM launch");
   if (copy_back) {
     cuda_check(cudaMemcpyAsync(out.data_ptr(), out_->local(), out_bytes, cudaMemcpyDeviceToDevice,
                                stream()),
@@ -563,16 +620,14 @@ void OverlapImpl::GemmAll2AllFused(at::Tensor A, at::Tensor B, at::Tensor D, int
   }
   a2a_tab_ = tab.to(at::Device(at::kCUDA, device_));
 
-  ++epoch_;
-  ++a2a_epoch_;
   set_l2_hints(&p, opt_l2_hints_ != 0);
   p.out_mode = kOutAll2All;
   p.rldn = 1;
   p.comm = kCommFusedA2A;
   p.ws = world_;
   p.rank_base = rank_;
-  p.epoch_done = static_cast<uint32_t>(world_) * epoch_;
-  p.epoch_ready = static_cast<uint32_t>(world_) * a2a_epoch_;
+  p.epoch_done = static_cast<uint32_t>(world_) * (epoch_ + 1);
+  p.epoch_ready = static_cast<uint32_t>(world_) * (a2a_epoch_ + 1);
   p.timeout_ns = static_cast<uint64_t>(opt_timeout_ms_) * 1000000ull;
   p.a2a_tab = a2a_tab_.data_ptr<int>();
   p.status[0] = status_.data_ptr<int>();
@@ -584,7 +639,15 @@ void OverlapImpl::GemmAll2AllFused(at::Tensor A, at::Tensor B, at::Tensor D, int
     p.ready[r] = reinterpret_cast<uint32_t*>(sig + kSignalReadyOffset);
   }
   const int grid = std::max(1, std::min(gemm_max_resident_ctas(algo, bf16, false), p.num_tiles));
-  cuda_check(launch_gemm(algo, bf16, false, maps, p, grid, 1, false, stream()), "all-to-all GEMM launch");
+  // the call numbers advance only with a launch that happened (see run_fused)
+  ++epoch_;
+  ++a2a_epoch_;
+  const cudaError_t launched = launch_gemm(algo, bf16, false, maps, p, grid, 1, false, stream());
+  if (launched != cudaSuccess) {
+    --epoch_;
+    --a2a_epoch_;
+  }
+  cuda_check(launched, "all-to-all GEMM launch");
   if (copy_back && recv_bytes > 0) {
     cuda_check(cudaMemcpyAsync(D.data_ptr(), out_->local(), recv_bytes, cudaMemcpyDeviceToDevice, stream()),
                "cudaMemcpyAsync");
@@ -601,12 +664,98 @@ int* mm_ptr(const at::Tensor& MM) {
 }
 }  // namespace
 
+// Sizes of the index arrays of an overlap call.  Every one of them is used as an address
+// offset by the kernel, so a short array is an out-of-bounds access on the device: refuse it
+// here.  With option "validate" the values are checked too (one device-to-host copy each).
+void OverlapImpl::check_overlap_args(const char* what, int M, int N, int algo, const at::Tensor& MM,
+                                     const at::Tensor& RA, const at::Tensor* RE, int64_t rLDN,
+                                     const at::Tensor& cSEG_CPU, const at::Tensor& cSEG_GPU,
+                                     bool monitor, bool needs_counters) const {
+  FO_CHECK(algo >= 0 && algo < kNumAlgos, what, ": Algo ", algo, " out of range [0, ", kNumAlgos, ")");
+  const AlgoConfig c = algo_config(algo);
+  FO_CHECK(M % c.bm == 0 && N % c.bn == 0, what, ": M and N must be multiples of the tile (", c.bm, " x ", c.bn, ")");
+  const int64_t tn = N / c.bn;
+  const int64_t tiles = static_cast<int64_t>(M / c.bm) * tn;
+  FO_CHECK(rLDN >= 1, what, ": rLDN must be at least 1");
+  if (RA.defined() && RA.numel() > 0) {
+    FO_CHECK(RA.numel() >= tiles, what, ": RA has ", RA.numel(), " entries, the shape has ", tiles, " tiles");
+  }
+  int64_t groups = 0;
+  if (cSEG_GPU.defined() && cSEG_GPU.numel() > 0) {
+    groups = cSEG_GPU.numel();
+    FO_CHECK(groups <= tiles, what, ": more wave groups (", groups, ") than tiles (", tiles, ")");
+    if (cSEG_CPU.defined() && cSEG_CPU.numel() > 0) {
+      FO_CHECK(!cSEG_CPU.is_cuda() && cSEG_CPU.scalar_type() == at::kInt && cSEG_CPU.is_contiguous(),
+               what, ": cSEG_CPU must be a contiguous int32 host tensor");
+      FO_CHECK(cSEG_CPU.numel() == groups, what, ": cSEG_CPU and cSEG_GPU differ in length");
+      const int* seg = cSEG_CPU.data_ptr<int>();
+      int64_t sum = 0;
+      for (int64_t i = 0; i < groups; ++i) {
+        FO_CHECK(seg[i] > 0, what, ": cSEG_CPU[", i, "] = ", seg[i], " (groups hold at least one tile)");
+        sum += seg[i];
+      }
+      FO_CHECK(sum == tiles, what, ": cSEG_CPU sums to ", sum, ", the shape has ", tiles, " tiles");
+    }
+  }
+  if (monitor) {
+    // row 0: counters (the completion counter is its last word), rows 1..: one word per tile
+    FO_CHECK(MM.defined() && MM.numel() >= tn + tiles, what, ": in monitor mode MM needs (TM + 1) * TN = ",
+             tn + tiles, " entries, it has ", MM.defined() ? MM.numel() : 0);
+    FO_CHECK(!needs_counters || groups < tn, what, ": in monitor mode the group counters (", groups,
+             ") must leave the last word of MM's first row (TN = ", tn, ") to the completion counter");
+  } else if (needs_counters) {
+    FO_CHECK(MM.defined() && MM.numel() >= std::max<int64_t>(groups, 1), what, ": MM has fewer counters (",
+             MM.defined() ? MM.numel() : 0, ") than there are wave groups (", groups, ")");
+  }
+  if (RE != nullptr) {
+    const int64_t rows = static_cast<int64_t>(M) * tn;  // rows of the [M * N / BN, BN] view
+    FO_CHECK(RE->defined() && RE->numel() >= rows, what, ": RE needs M * N / BN = ", rows, " entries, it has ",
+             RE->defined() ? RE->numel() : 0);
+  }
+  if (opt_validate_ == 0) return;
+  // Deep validation (debug builds switch it on by default): the values, read back from the device.
+  if (RA.defined() && RA.numel() > 0) {
+    const at::Tensor h = RA.reshape({-1}).slice(0, 0, tiles).cpu();
+    std::vector<char> seen(static_cast<size_t>(tiles), 0);
+    const int* v = h.data_ptr<int>();
+    for (int64_t t = 0; t < tiles; ++t) {
+      FO_CHECK(v[t] >= 0 && v[t] < tiles, what, ": RA[", t, "] = ", v[t], " is not a tile position in [0, ", tiles, ")");
+      FO_CHECK(!seen[v[t]], what, ": RA is not a permutation (position ", v[t], " appears twice)");
+      seen[v[t]] = 1;
+    }
+  }
+  if (groups > 0) {
+    const at::Tensor h = cSEG_GPU.cpu();
+    const int* v = h.data_ptr<int>();
+    int64_t sum = 0;
+    for (int64_t i = 0; i < groups; ++i) {
+      FO_CHECK(v[i] > 0, what, ": cSEG_GPU[", i, "] = ", v[i]);
+      sum += v[i];
+    }
+    FO_CHECK(sum == tiles, what, ": cSEG_GPU sums to ", sum, ", the shape has ", tiles, " tiles");
+    if (cSEG_CPU.defined() && cSEG_CPU.numel() == groups) {
+      const int* c = cSEG_CPU.data_ptr<int>();
+      for (int64_t i = 0; i < groups; ++i) FO_CHECK(c[i] == v[i], what, ": cSEG_CPU and cSEG_GPU differ at ", i);
+    }
+  }
+  if (RE != nullptr) {
+    const int64_t rows = static_cast<int64_t>(M) * tn;
+    const at::Tensor h = RE->reshape({-1}).slice(0, 0, rows).cpu();
+    const int* v = h.data_ptr<int>();
+    for (int64_t i = 0; i < rows; ++i) {
+      FO_CHECK(v[i] >= 0 && v[i] < rows, what, ": RE[", i, "] = ", v[i], " is not a row in [0, ", rows, ")");
+    }
+  }
+}
+
 void OverlapImpl::GemmAllReduceOverlap(at::Tensor A, at::Tensor B, at::Tensor C, at::Tensor MM,
                                        at::Tensor RA, int64_t rLDN, at::Tensor cSEG_CPU,
                                        at::Tensor cSEG_GPU, int64_t Algo, bool if_monitor) {
   NvtxRange nvtx_range("flashoverlap::gemm_allreduce_overlap");
   const GemmShape s = check_operands(A, B);
   check_out(C, A, static_cast<int64_t>(s.M) * s.N, "C");
+  check_overlap_args("gemm_allreduce_overlap", s.M, s.N, static_cast<int>(Algo), MM, RA, nullptr, rLDN, cSEG_CPU,
+                     cSEG_GPU, if_monitor, opt_mode_ == 1 && world_ > 1);
   const AlgoConfig c = algo_config(static_cast<int>(Algo));
   const int tn = s.N / c.bn;
   const int* ra = int_ptr_or_null(RA, "RA");
@@ -636,6 +785,9 @@ void OverlapImpl::GemmReduceScatterOverlap(at::Tensor A, at::Tensor B, at::Tenso
   NvtxRange nvtx_range("flashoverlap::gemm_reducescatter_overlap");
   const GemmShape s = check_operands(A, B);
   check_out(D, A, static_cast<int64_t>(s.M) * s.N / world_, "D");
+  const bool gated = opt_mode_ == 1 && world_ > 1;
+  check_overlap_args("gemm_reducescatter_overlap", s.M, s.N, static_cast<int>(Algo), MM, RA, gated ? &RE : nullptr,
+                     rLDN, cSEG_CPU, cSEG_GPU, if_monitor, gated);
   const AlgoConfig c = algo_config(static_cast<int>(Algo));
   const int tn = s.N / c.bn;
   const int* ra = int_ptr_or_null(RA, "RA");
@@ -674,7 +826,8 @@ void OverlapImpl::gated_overlap(int comm, at::Tensor A, at::Tensor B, at::Tensor
   const int* seg = cSEG_CPU.data_ptr<int>();
   const int ngroups = static_cast<int>(cSEG_CPU.numel());
   const int* cseg_gpu = int_ptr_or_null(cSEG_GPU, "cSEG_GPU");
-  FO_CHECK(cseg_gpu != nullptr && cSEG_GPU.numel() == ngroups, "cSEG_GPU must mirror cSEG_CPU");
+  FO_CHECK(ngroups > 0 && cseg_gpu != nullptr && cSEG_GPU.numel() == ngroups,
+           "the counter-gated mode needs wave groups: cSEG_CPU and its device copy cSEG_GPU");
   int* mm = mm_ptr(MM);
   FO_CHECK(MM.numel() >= ngroups, "MM has fewer counters than there are groups");
   const bool rs = comm == kCommFusedRS;

@@ -77,6 +77,11 @@ class OverlapImpl : public torch::CustomClassHolder {
   // the owners fetch them, through the switch's reduction when the buffer has a multicast mapping),
   // "epi_bufs" (2 | 4: fused kernels with four epilogue chunk buffers and one operand stage fewer;
   // their push warp keeps three chunks of stores in flight instead of waiting for each),
+  // "validate" (1: overlap calls also check the values of RA / RE / cSEG_GPU - permutation, range,
+  // sum - at the price of a device-to-host copy per call; on by default in a -DFO_DEBUG build),
+  // "tma_out" (1: plain GEMMs with a row-major or tile-contiguous output store finished chunks
+  // with TMA tensor stores; 0: per-thread 16-byte stores; -1, the default: TMA for the kernels
+  // whose epilogue overlaps the next main loop, per-thread stores for the 256 x 256-per-CTA ones),
   // "diag" (timing studies only - results are wrong: 1 skips the reducers' memory traffic, 2 the
   // push stores, 4 the reducers' arrival waits; shows which part of the collective is exposed.
   // After runs with bit 4, synchronise all ranks and call reset_status() before normal calls:
@@ -107,7 +112,20 @@ class OverlapImpl : public torch::CustomClassHolder {
   // Status words written by device-side waits that gave up (all zero when healthy).
   std::vector<int64_t> ReadStatus();
   void CheckStatus();  // throws with a description when the status is not ok
-  void ResetStatus();  // clears status and re-arms flags after a reported failure
+  // Clears the status words and this rank's own arrival counters after a reported failure that
+  // stayed local (a bounded wait inside one GPU).  It does not touch the cross-rank state: after a
+  // failure in which the ranks fell out of step (a peer skipped a call, a cross-GPU wait gave
+  // up) call resync() on every rank instead.
+  void ResetStatus();
+  // Waits on the caller's stream until MM[index] == target and resets it to 0 (the gated path's
+  // wait kernel as a call of its own); after "timeout_ms" it gives up and this object's status
+  // words say so (check_status then raises).
+  void WaitFlag(int64_t target, at::Tensor MM, int64_t index);
+  // Collective: every rank waits for its stream, all ranks meet (NCCL), each clears its whole
+  // signal region (arrival, done and ready counters) and status words, all meet again, and the
+  // call numbering restarts.  Brings a group of objects back in step after a fused call that
+  // some rank missed or gave up in; no fused call may be in flight on any rank.
+  void Resync();
 
  private:
   struct FusedArgs;
@@ -121,6 +139,9 @@ class OverlapImpl : public torch::CustomClassHolder {
                      at::Tensor MM, at::Tensor RA, at::Tensor RE, int64_t rLDN,
                      at::Tensor cSEG_CPU, at::Tensor cSEG_GPU, int64_t Algo, bool monitor);
   void ensure_fused_buffers(size_t stage_bytes, size_t nflags, bool pull);
+  void check_overlap_args(const char* what, int M, int N, int algo, const at::Tensor& MM, const at::Tensor& RA,
+                          const at::Tensor* RE, int64_t rLDN, const at::Tensor& cSEG_CPU, const at::Tensor& cSEG_GPU,
+                          bool monitor, bool needs_counters) const;
   void ensure_comm_stream();
   cudaStream_t stream() const;
   ncclDataType_t nccl_dtype(const at::Tensor& t) const;
@@ -157,6 +178,12 @@ class OverlapImpl : public torch::CustomClassHolder {
   int64_t opt_push_lag_ = 0;  // 0: chosen from K
   int64_t opt_diag_ = 0;         // timing studies only (results are wrong): see GemmParams::diag
   int64_t opt_epi_bufs_ = 2;     // epilogue chunk buffers of the fused kernels (2 or 4)
+#ifdef FO_DEBUG
+  int64_t opt_validate_ = 1;     // debug builds check the values of RA / RE / cSEG on every overlap call
+#else
+  int64_t opt_validate_ = 0;     // 1: also check the VALUES of RA / RE / cSEG_GPU (a device-to-host copy per call)
+#endif
+  int64_t opt_tma_out_ = -1;     // plain kernels' stores: 1 TMA tensor stores, 0 per-thread stores, -1 by kernel
   int64_t opt_stage_local_ = 0;  // 1: pull protocol (partials staged locally, owners fetch them)
   int64_t opt_l2_hints_ = 0;  // measured: priorities raise DRAM traffic on B200, off by default
 };

@@ -23,8 +23,7 @@ from flashoverlap_b200.utils import config
 def worker(rank, world, args):
     dt = torch.bfloat16 if args.dtype == "bf16" else torch.float16
     M, N, K = args.m, args.n, args.k
-    path = config.config_path(M, N, K, directory=args.path)
-    cfg = config.load_config(path) if path.exists() and config.is_tuned(config.load_config(path)) else \
+    cfg = config.load_tuned(M, N, K, tp=world, comm_op="all_reduce", directory=args.path) or \
         config.default_solution(M, N, args.algo)
     dev = torch.device("cuda", torch.cuda.current_device())
     g = torch.Generator(device=dev).manual_seed(100 + rank)

@@ -82,10 +82,8 @@ def _nccl_paths() -> tuple[str, str]:
     return "/usr/include", "/usr/lib/x86_64-linux-gnu"
 
 
-def build(force: bool = False, verbose: bool = False) -> Path:
-    """Compiles every source for sm_100a and places the library in-tree."""
-    if is_current() and not force:
-        return lib_path()
+def _compile(verbose: bool = False) -> None:
+    """Compiles the sources into the build directory (run in a child process by build())."""
     from torch.utils import cpp_extension
 
     build_dir = _ROOT / "build" / _EXT_NAME
@@ -103,12 +101,29 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         is_python_module=False,
         verbose=verbose,
     )
-    built = build_dir / (_EXT_NAME + ".so")
+
+
+def build(force: bool = False, verbose: bool = False) -> Path:
+    """Compiles every source for sm_100a and places the library in-tree.
+
+    The compiler runs in a child process: ``cpp_extension.load`` maps the image it has just
+    built (in the build directory) into the process that called it, and a process that later
+    loads the in-tree copy as well would hold two images of the library - two sets of op
+    registrations and two copies of every device symbol.  This process only ever maps
+    ``lib_path()``, so a ``ctypes.CDLL(lib_path())`` gets the handle torch already holds."""
+    if is_current() and not force:
+        return lib_path()
+    import subprocess
+    import sys
+
+    subprocess.run([sys.executable, "-c",
+                    f"import sys; sys.path.insert(0, {str(_ROOT)!r}); "
+                    f"from flashoverlap_b200 import _build; _build._compile({bool(verbose)!r})"],
+                   check=True, cwd=str(_ROOT))
+    built = _ROOT / "build" / _EXT_NAME / (_EXT_NAME + ".so")
     _LIB_DIR.mkdir(parents=True, exist_ok=True)
     shutil.copy2(built, lib_path())
     write_stamp()
-    global _loaded
-    _loaded = True  # cpp_extension.load already registered the ops in this process
     return lib_path()
 
 
@@ -124,8 +139,6 @@ def load(allow_build: bool = True) -> Path:
             raise RuntimeError(
                 f"{lib_path()} is missing or stale; run `python -c 'import __graft_entry__ as g; g.build()'`")
         build()
-        if _loaded:
-            return lib_path()
     torch.ops.load_library(str(lib_path()))
     _loaded = True
     return lib_path()

@@ -51,8 +51,16 @@ def _child(rank: int, world: int, port: int, fn: Callable, args: tuple, out_path
         # The peers may be blocked in a collective that this rank will never join, and a clean
         # process-group shutdown would wait for them: report and leave at once, the parent then
         # terminates the other ranks.
+        import time
         import traceback
         traceback.print_exc()
+        # Peers' kernels may still address this rank's memory (peer or multicast mappings);
+        # their device waits are bounded, so give them a moment to run out before the mappings go.
+        try:
+            torch.cuda.synchronize()
+        except Exception:
+            pass
+        time.sleep(float(os.environ.get("FLASHOVERLAP_EXIT_GRACE_S", "3")))
         os._exit(1)
     if rank == 0:
         torch.save(res, out_path)

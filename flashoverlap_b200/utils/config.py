@@ -104,6 +104,39 @@ def is_tuned(cfg: dict) -> bool:
     return "hint" in cfg and "cSeg" in cfg and not isinstance(cfg.get("Algo"), list)
 
 
+def matches(cfg: dict, tp: Optional[int] = None, comm_op: Optional[str] = None, mode: Optional[str] = None) -> bool:
+    """Whether a tuned config was searched for this use.  The file name carries only (M, N, K,
+    gpu); ``search`` also records the world size, the collective and the overlap mechanism the
+    grouping was tuned for.  A key the file does not carry (a config written by the reference's
+    tools) matches anything; a key it carries must agree with the call."""
+    for key, want in (("tp", tp), ("comm_op", comm_op), ("mode", mode)):
+        if want is not None and key in cfg and cfg[key] != want:
+            return False
+    return True
+
+
+def load_tuned(M: int, N: int, K: int, tp: Optional[int] = None, comm_op: Optional[str] = None,
+               mode: Optional[str] = None, gpu: Optional[str] = None,
+               directory: Optional[os.PathLike] = None, warn: bool = True) -> Optional[dict]:
+    """The tuned config of a shape if there is one AND it was tuned for this world size,
+    collective and mechanism; otherwise None (callers then fall back to ``default_solution``).
+    A config tuned for the counter-gated all-reduce is never silently used for the fused
+    reduce-scatter of the same shape."""
+    path = config_path(M, N, K, gpu, directory)
+    if not path.exists():
+        return None
+    cfg = load_config(path)
+    if not is_tuned(cfg):
+        return None
+    if not matches(cfg, tp, comm_op, mode):
+        if warn:
+            import warnings
+            have = {k: cfg.get(k) for k in ("tp", "comm_op", "mode") if k in cfg}
+            warnings.warn(f"{path} was tuned for {have}, not for tp={tp} comm_op={comm_op} mode={mode}: ignored")
+        return None
+    return cfg
+
+
 def default_solution(M: int, N: int, algo: int = 0, wave_size: int = 148, groups: Optional[List[int]] = None) -> dict:
     """A usable config without any tuning run: analytic hint and one wave per group."""
     from . import layout

@@ -37,13 +37,20 @@ REP = 200
 def worker(rank, world, args):
     dt = dtype_of(args.dtype)
     impl = bootstrap.make_overlap_impl(rank, world)
-    impl.set_option("timeout_ms", 20000)
+    impl.set_option("timeout_ms", args.timeout_ms)
     base = bootstrap.make_baseline_impl(rank, world)
-    path = config.config_path(args.m, args.n, args.k, directory=args.path)
-    if os.path.exists(path) and config.is_tuned(config.load_config(path)):
-        cfg = config.load_config(path)
-    else:
-        cfg = config.default_solution(args.m, args.n, args.algo)
+
+    def checked(fn):
+        """One call, then the device status: a protocol failure stops the test here instead of
+        running into the bounded waits again on every timed iteration."""
+        fn()
+        torch.cuda.synchronize()
+        impl.check_status()
+        return fn
+
+    # a tuned config counts only if it was searched for this world size and collective
+    cfg = config.load_tuned(args.m, args.n, args.k, tp=world, comm_op=args.comm_op, directory=args.path) or \
+        config.default_solution(args.m, args.n, args.algo)
     algo = cfg["Algo"]
     sm, margin = impl.get_option("sm_count"), impl.get_option("sm_margin")
     res = {"M": args.m, "N": args.n, "K": args.k, "tp": world, "comm_op": args.comm_op, "Algo": algo}
@@ -62,20 +69,20 @@ def worker(rank, world, args):
         res["baseline_ms"] = perf_ms(lambda: base.gemm_reducescatter(wl.A, wl.B, full, wl.D), WARM_UP, args.reps, f)
     res["nonoverlap_ms"] = perf_ms(wl.run_nonoverlap, WARM_UP, args.reps, f)
     wl.set_cseg([1] * wl.tiles if "cSeg" not in cfg or cfg.get("mode") == "gated" else cfg["cSeg"])
-    res["fused_ms"] = perf_ms(wl.run, WARM_UP, args.reps, f)
+    res["fused_ms"] = perf_ms(checked(wl.run), WARM_UP, args.reps, f)
     if world > 1 and args.pull:
         # pull protocol: partials stay on the producing GPU; owners fetch them with peer loads,
         # then (staging with a multicast mapping) with one switch-side reduction per vector
         from flashoverlap_b200.parallel import symm
         impl.set_option("stage_local", 1)
-        res["fused_pull_peer_ms"] = perf_ms(wl.run, WARM_UP, args.reps, f)
+        res["fused_pull_peer_ms"] = perf_ms(checked(wl.run), WARM_UP, args.reps, f)
         _, switch = symm.alloc_stage(impl, args.m, args.n, dt)
         if switch:
-            res["fused_pull_switch_ms"] = perf_ms(wl.run, WARM_UP, args.reps, f)
+            res["fused_pull_switch_ms"] = perf_ms(checked(wl.run), WARM_UP, args.reps, f)
         impl.set_option("stage_local", 0)
     if world > 1 and args.epi4:
         impl.set_option("epi_bufs", 4)
-        res["fused_epi4_ms"] = perf_ms(wl.run, WARM_UP, args.reps, f)
+        res["fused_epi4_ms"] = perf_ms(checked(wl.run), WARM_UP, args.reps, f)
         impl.set_option("epi_bufs", 2)
     if world > 1:
         wl.mode = "gated"
@@ -127,6 +134,7 @@ def main():
     ap.add_argument("--path", default=None)
     ap.add_argument("--reps", type=int, default=REP)
     ap.add_argument("--flush", action="store_true", help="flush L2 between timed iterations")
+    ap.add_argument("--timeout_ms", type=int, default=5000, help="bound of the kernels' cross-GPU waits")
     ap.add_argument("--epi4", action="store_true",
                     help="also time the fused kernel built with four epilogue chunk buffers (option epi_bufs)")
     ap.add_argument("--pull", action="store_true",

@@ -2,6 +2,7 @@
 import os
 import socket
 import tempfile
+import time
 import traceback
 
 import torch
@@ -13,6 +14,20 @@ def free_port() -> int:
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
         return s.getsockname()[1]
+
+
+def _leave_together(rank, world, result_dir, ok, limit_s=20.0):
+    """A rank must not unmap its device memory while a peer's kernel may still address it (peer
+    or multicast mappings): before leaving, every rank drops a marker and waits - bounded - until
+    all ranks have dropped theirs.  Kernels' own waits are bounded by a few seconds, so after the
+    limit nothing of the other ranks is in flight either way."""
+    open(os.path.join(result_dir, f"r{rank}.{'left' if ok else 'failed'}"), "w").close()
+    t0 = time.time()
+    while time.time() - t0 < limit_s:
+        if all(os.path.exists(os.path.join(result_dir, f"r{r}.left")) or
+               os.path.exists(os.path.join(result_dir, f"r{r}.failed")) for r in range(world)):
+            return
+        time.sleep(0.05)
 
 
 def _entry(rank, world, backend, port, fn, args, result_dir, timeout_s):
@@ -28,11 +43,15 @@ def _entry(rank, world, backend, port, fn, args, result_dir, timeout_s):
                                 timeout=datetime.timedelta(seconds=timeout_s))
         out = fn(rank, world, *args)
         torch.save(out, os.path.join(result_dir, f"r{rank}.pt"))
+        if backend == "nccl":
+            torch.cuda.synchronize()
+        _leave_together(rank, world, result_dir, True)
         dist.barrier()
         dist.destroy_process_group()
     except Exception:
         with open(os.path.join(result_dir, f"r{rank}.err"), "w") as f:
             f.write(traceback.format_exc())
+        _leave_together(rank, world, result_dir, False)
         raise
 
 

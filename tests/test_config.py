@@ -69,3 +69,27 @@ def test_gen_config_csv_rows_map_back_to_algos(tmp_path, monkeypatch):
         w.writerow({"cta_m": 64, "cta_n": 64, "cta_k": 32, "stages": 3, "raster": 1, "cta_group": 1, "runtime": 0.5})
     assert gen_config.candidates_from_csv(str(path)) == algos      # the unknown row is skipped
     sys.modules.pop("gen_config", None)
+
+
+def test_tuned_config_is_used_only_for_what_it_was_tuned_for(tmp_path):
+    """A config searched for the counter-gated all-reduce at tp4 must not be picked up by a fused
+    reduce-scatter (or another world size) of the same shape; files without the keys match."""
+    import warnings
+    from flashoverlap_b200.utils import config
+    M, N, K = 512, 1024, 256
+    path = config.config_path(M, N, K, "b200", tmp_path)
+    config.save_solution(path, 128, 256, 0.1, 0, list(range(16)), [8, 8], 1, tp=4, comm_op="all_reduce", mode="gated")
+    assert config.load_tuned(M, N, K, tp=4, comm_op="all_reduce", mode="gated", gpu="b200", directory=tmp_path)["cSeg"] == [8, 8]
+    assert config.load_tuned(M, N, K, tp=4, comm_op="all_reduce", gpu="b200", directory=tmp_path) is not None
+    with warnings.catch_warnings(record=True) as w:
+        warnings.simplefilter("always")
+        assert config.load_tuned(M, N, K, tp=4, comm_op="reduce_scatter", gpu="b200", directory=tmp_path) is None
+        assert config.load_tuned(M, N, K, tp=8, comm_op="all_reduce", gpu="b200", directory=tmp_path) is None
+        assert config.load_tuned(M, N, K, tp=4, comm_op="all_reduce", mode="fused", gpu="b200", directory=tmp_path) is None
+        assert len(w) == 3 and "ignored" in str(w[0].message)
+    # a stage-1 file (lists) is not a tuned config; a file without the optional keys matches any use
+    config.save_stage1(path, [128], [256], [0.1], [0])
+    assert config.load_tuned(M, N, K, tp=4, comm_op="all_reduce", gpu="b200", directory=tmp_path) is None
+    config.save_solution(path, 128, 256, 0.1, 0, list(range(16)), [16], 1)
+    assert config.load_tuned(M, N, K, tp=2, comm_op="reduce_scatter", mode="fused", gpu="b200", directory=tmp_path) is not None
+    assert config.load_tuned(M + 128, N, K, gpu="b200", directory=tmp_path) is None

@@ -7,7 +7,6 @@ import torch
 from flashoverlap_b200 import ops
 from flashoverlap_b200.utils import config, layout
 
-from tests.conftest import experimental
 
 pytestmark = pytest.mark.gpu
 
@@ -140,8 +139,12 @@ def _check_hint(cuda, impl, algo):
     waves_measured = (order // grid)
     waves_analytic = torch.empty(tm * tn, dtype=torch.long)
     waves_analytic[torch.tensor(hint)] = torch.arange(tm * tn) // grid
-    # tiles of the same CTA finish in order, so wave membership can differ only at wave edges
-    agree = (waves_measured == waves_analytic).float().mean().item()
+    # Tiles of the same CTA finish in order, so a tile can only be observed one wave away from
+    # its analytic wave: when a fast CTA retires its next tile before a slow CTA has retired its
+    # current one, the two swap completion ranks across the wave edge.  Nothing may be further off.
+    diff = (waves_measured - waves_analytic).abs()
+    assert diff.max().item() <= 1, diff.max().item()
+    agree = (diff == 0).float().mean().item()
     assert agree > 0.9, agree
 
 
@@ -206,7 +209,6 @@ def test_fused_loopback_pull_protocol(cuda, comm_op):
                    dt=torch.float16, stage_local=True)
 
 
-@experimental
 @pytest.mark.parametrize("ws,algo,dt", [(2, 0, torch.bfloat16), (4, 2, torch.bfloat16), (8, 0, torch.float16)])
 def test_gemm_all2all_loopback(cuda, ws, algo, dt):
     """GEMM whose epilogue stores each row into its destination rank's receive buffer."""
@@ -227,7 +229,6 @@ def test_gemm_all2all_loopback(cuda, ws, algo, dt):
             assert (out[r][:n].float() - want[r]).abs().max().item() <= _tol(want[r]), r
 
 
-@experimental
 @pytest.mark.parametrize("ws,algo,strided,dt", [(2, 0, True, torch.bfloat16), (4, 2, False, torch.bfloat16),
                                                (8, 0, True, torch.float16)])
 def test_reducescatter_rmsnorm_tail_loopback(cuda, ws, algo, strided, dt):
@@ -248,7 +249,6 @@ def test_reducescatter_rmsnorm_tail_loopback(cuda, ws, algo, strided, dt):
         assert (out[r].float() - expect).abs().max().item() <= 0.03 * expect.abs().max().item(), r
 
 
-@experimental
 def test_fused_loopback_timeline(cuda):
     """The tracing build of the fused kernel stamps every tile in order of its life cycle."""
     from flashoverlap_b200.utils import trace
@@ -271,7 +271,6 @@ def test_fused_loopback_timeline(cuda):
     assert s["reduce"]["tiles"] == tiles and s["span"]["us"] > 0
 
 
-@experimental
 @pytest.mark.parametrize("comm_op", ["all_reduce", "reduce_scatter"])
 def test_fused_loopback_four_chunk_buffers(cuda, comm_op):
     """Build with four epilogue chunk buffers: the push warp keeps three chunks of stores in flight."""
@@ -323,3 +322,132 @@ def test_world1_reference_api(cuda, impl):
     assert (d.float() - ref).abs().max().item() <= _tol(ref)
     base.cublas_gemm(a, b, d); base.nccl_allreduce(d); base.nccl_reducescatter(d)
     assert impl.read_status()[0] == 0
+
+
+def test_overlap_call_rejects_short_index_arrays(cuda, impl):
+    """RA, MM, cSEG are used as address offsets by the kernel: arrays that are too short for the
+    shape are refused on the host, before any launch."""
+    M, N, K, algo = 512, 1024, 128, 0
+    tm, tn = M // 128, N // 256
+    tiles = tm * tn
+    a, b = _rand((M, K), torch.bfloat16, cuda), _rand((N, K), torch.bfloat16, cuda)
+    c = torch.zeros(M, N, device=cuda, dtype=torch.bfloat16)
+    RA = torch.arange(tiles, device=cuda, dtype=torch.int32)
+    mm = torch.zeros(tm + 1, tn, device=cuda, dtype=torch.int32)
+    e = torch.empty(0, dtype=torch.int32)
+    eg = e.to(cuda)
+    with pytest.raises(RuntimeError, match="RA has"):
+        impl.gemm_allreduce_overlap(a, b, c, mm, RA[: tiles - 1], 1, e, eg, algo, False)
+    with pytest.raises(RuntimeError, match="monitor mode MM needs"):
+        impl.gemm_allreduce_overlap(a, b, c, mm[:1], RA, 1, e, eg, algo, True)
+    bad = torch.tensor([tiles - 1, 2], dtype=torch.int32)
+    with pytest.raises(RuntimeError, match="cSEG_CPU sums to"):
+        impl.gemm_allreduce_overlap(a, b, c, mm, RA, 1, bad, bad.to(cuda), algo, False)
+    with pytest.raises(RuntimeError, match="differ in length"):
+        impl.gemm_allreduce_overlap(a, b, c, mm, RA, 1, bad[:1], bad.to(cuda), algo, False)
+    with pytest.raises(RuntimeError, match="out of range"):
+        impl.gemm_allreduce_overlap(a, b, c, mm, RA, 1, e, eg, 999, False)
+    with pytest.raises(RuntimeError, match="RA has"):
+        impl.gemm_reducescatter_overlap(a, b, c, c, mm, RA[:2], eg, 1, e, eg, algo, False)
+    impl.check_status()
+    impl.gemm_allreduce_overlap(a, b, c, mm, RA, 1, e, eg, algo, False)      # the object is still usable
+    ref = a.float() @ b.float().t()
+    assert (c.float() - ref).abs().max().item() <= _tol(ref)
+
+
+def test_bad_ra_value_is_reported_not_followed(cuda):
+    """A tile position outside [0, tiles) in RA: with option ``validate`` the host refuses the call;
+    without it the kernel reports kStatusBadArgument, keeps every access inside the buffers (the
+    tile is stored at its natural position instead) and the context stays usable."""
+    i = ops.OverlapImpl()
+    i.nccl_init(0, 1, [0] * 16)
+    M, N, K, algo = 512, 1024, 128, 0
+    tiles = (M // 128) * (N // 256)
+    a, b = _rand((M, K), torch.bfloat16, cuda), _rand((N, K), torch.bfloat16, cuda)
+    c = torch.zeros(M, N, device=cuda, dtype=torch.bfloat16)
+    mm = torch.zeros(1, N // 256, device=cuda, dtype=torch.int32)
+    e = torch.empty(0, dtype=torch.int32)
+    RA = torch.arange(tiles, device=cuda, dtype=torch.int32)
+    RA[3] = tiles + 7
+    i.set_option("validate", 1)
+    with pytest.raises(RuntimeError, match="not a tile position"):
+        i.gemm_allreduce_overlap(a, b, c, mm, RA, 1, e, e.to(cuda), algo, False)
+    dup = torch.arange(tiles, device=cuda, dtype=torch.int32)
+    dup[5] = 4
+    with pytest.raises(RuntimeError, match="not a permutation"):
+        i.gemm_allreduce_overlap(a, b, c, mm, dup, 1, e, e.to(cuda), algo, False)
+    i.set_option("validate", 0)
+    i.gemm_allreduce_overlap(a, b, c, mm, RA, 1, e, e.to(cuda), algo, False)
+    torch.cuda.synchronize()
+    st = i.read_status()
+    assert st[0] == 9 and st[1] == 1 and st[2] == 3 and st[3] == tiles + 7, st      # bad argument: RA[3]
+    with pytest.raises(RuntimeError, match="bad argument"):
+        i.check_status()
+    i.reset_status()
+    RA[3] = 3
+    c.fill_(float("nan"))
+    i.gemm_allreduce_overlap(a, b, c, mm, RA, 1, e, e.to(cuda), algo, False)
+    i.check_status()
+    ref = a.float() @ b.float().t()
+    got = ops.unreorder(c, M, N, 128, 256, RA)
+    assert (got.float() - ref).abs().max().item() <= _tol(ref)
+
+
+def test_check_status_raises_with_decoded_message(cuda):
+    """A device wait that runs out, written into an OverlapImpl's own status words: read_status
+    returns the code and its arguments, check_status raises with the decoded text, reset_status
+    clears it.  The failure is made on the host: a counter that nothing ever sets."""
+    i = ops.OverlapImpl()
+    i.nccl_init(0, 1, [0] * 16)
+    i.set_option("timeout_ms", 50)
+    mm = torch.zeros(4, device=cuda, dtype=torch.int32)
+    mm[2] = 3
+    i.wait_flag(3, mm, 2)                              # satisfied at once, counter reset by the wait
+    torch.cuda.synchronize()
+    i.check_status()
+    assert mm[2].item() == 0
+    t0 = time.time()
+    i.wait_flag(3, mm, 1)                              # nothing sets counter 1: the wait gives up
+    torch.cuda.synchronize()
+    assert time.time() - t0 < 5.0
+    st = i.read_status()
+    assert st[0] == 8 and st[1] == 1, st               # kStatusTimeoutWaitKernel, counter index
+    with pytest.raises(RuntimeError, match="counting wait kernel"):
+        i.check_status()
+    i.reset_status()
+    i.check_status()
+    with pytest.raises(RuntimeError, match="outside MM"):
+        i.wait_flag(1, mm, 9)
+
+
+@pytest.mark.parametrize("algo", [0, 1, 2, 3, 22])
+def test_plain_epilogues_agree(cuda, algo):
+    """TMA tensor stores and per-thread stores must write the same bytes, in the row-major and the
+    tile-contiguous layout (rLDN 1 and 2)."""
+    i = ops.OverlapImpl()
+    i.nccl_init(0, 1, [0] * 16)
+    M, N, K = 1024, 2048, 192
+    p = config.algo_params(algo)
+    tm, tn = M // p["BM"], N // p["BN"]
+    a, b = _rand((M, K), torch.bfloat16, cuda), _rand((N, K), torch.bfloat16, cuda)
+    ref = a.float() @ b.float().t()
+    e = torch.empty(0, dtype=torch.int32)
+    outs = {}
+    for tma in (1, 0):
+        i.set_option("tma_out", tma)
+        c = torch.full((M, N), float("nan"), device=cuda, dtype=torch.bfloat16)
+        i.cutlass_gemm(a, b, c, algo)
+        assert (c.float() - ref).abs().max().item() <= _tol(ref)
+        outs[("nat", tma)] = c
+        for rldn in (1, 2):
+            RA = torch.randperm(tm * tn, device=cuda, dtype=torch.int32, generator=torch.Generator(device=cuda).manual_seed(rldn))
+            mm = torch.zeros(tm + 1, tn, device=cuda, dtype=torch.int32)
+            c2 = torch.full((M, N), float("nan"), device=cuda, dtype=torch.bfloat16)
+            i.gemm_allreduce_overlap(a, b, c2, mm, RA.reshape(tm, tn), rldn, e, e.to(cuda), algo, True)
+            got = ops.unreorder(c2, M, N, p["BM"], p["BN"], RA.reshape(tm, tn), rldn)
+            assert (got.float() - ref).abs().max().item() <= _tol(ref)
+            assert torch.equal(mm[1:].flatten().sort().values, torch.arange(tm * tn, device=cuda, dtype=torch.int32))
+            outs[(rldn, tma)] = c2
+    i.check_status()
+    for key in ("nat", 1, 2):
+        assert torch.equal(outs[(key, 1)], outs[(key, 0)]), key

@@ -10,7 +10,6 @@ import torch
 import torch.distributed as dist
 
 from tests._mp import run_ranks
-from tests.conftest import experimental
 
 pytestmark = pytest.mark.gpu
 
@@ -143,7 +142,6 @@ def _pull_worker(rank, world):
     return res
 
 
-@experimental
 def test_pull_protocol_multi_gpu(lib):
     """Pull protocol over real NVLink: first with peer loads, then with the staging in
     multicast-mapped memory, where the owners' reducers sum with multimem.ld_reduce."""
@@ -182,7 +180,6 @@ def _all2all_worker(rank, world):
     return res
 
 
-@experimental
 def test_gemm_all2all_fused_multi_gpu(lib):
     world = _world()
     for r in run_ranks(_all2all_worker, world, "nccl"):
@@ -211,7 +208,6 @@ def _norm_tail_worker(rank, world):
     return res
 
 
-@experimental
 def test_reducescatter_rmsnorm_tail_multi_gpu(lib):
     world = _world()
     for r in run_ranks(_norm_tail_worker, world, "nccl"):
@@ -361,6 +357,18 @@ def _timeout_worker(rank, world):
             out["raised"] = True
         out["alive"] = float(torch.ones(8, device=dev).sum().item())
     dist.barrier()
+    # The ranks now disagree on the call number (rank 0 made a call that rank 1 never saw): every
+    # later fused call would time out.  resync() - collective - brings them back in step.
+    impl.set_option("timeout_ms", 5000)
+    impl.resync()
+    ref = A.float() @ B.float().t()
+    dist.all_reduce(ref)
+    for _ in range(2):
+        C.fill_(float("nan")); torch.cuda.synchronize(); dist.barrier()
+        impl.gemm_allreduce_fused(A, B, C, 0)
+    torch.cuda.synchronize(); dist.barrier()
+    out["after_resync_status"] = impl.read_status()[0]
+    out["after_resync_err"] = (C.float() - ref).abs().max().item() / (0.02 * ref.abs().max().item() + 1e-3)
     return out
 
 
@@ -373,3 +381,38 @@ def test_missing_peer_times_out_with_status(lib):
     assert r0["status"][0] in (5, 6, 7), r0          # a cross-GPU wait gave up
     assert r0["raised"] and r0["alive"] == 8.0
     assert r0["elapsed"] < 10.0
+    for r in res:
+        assert r["after_resync_status"] == 0 and r["after_resync_err"] <= 1.0, r
+
+
+def _rejected_call_worker(rank, world):
+    """A fused call that the host rejects after the collective set-up (a trace buffer too small
+    for the shape) must not advance the call number: the next call succeeds on every rank."""
+    dev = torch.device("cuda", rank)
+    impl = _setup(rank, world)
+    M, N, K = 512, 1024, 128
+    A, B = _rand((M, K), dev, 3 + rank), _rand((N, K), dev, 5 + rank)
+    ref = A.float() @ B.float().t()
+    dist.all_reduce(ref)
+    C = impl.symm_empty([M, N], "bfloat16")
+    impl.gemm_allreduce_fused(A, B, C, 0)
+    torch.cuda.synchronize(); dist.barrier()
+    impl.set_trace(torch.zeros(8, device=dev, dtype=torch.int64))      # far too small
+    raised = False
+    try:
+        impl.gemm_allreduce_fused(A, B, C, 0)
+    except RuntimeError as ex:
+        raised = "trace buffer" in str(ex)
+    impl.set_trace(torch.zeros(0, dtype=torch.int64))
+    for _ in range(2):
+        C.fill_(float("nan")); torch.cuda.synchronize(); dist.barrier()
+        impl.gemm_allreduce_fused(A, B, C, 0)
+    torch.cuda.synchronize(); dist.barrier()
+    return {"raised": raised, "status": impl.read_status()[0],
+            "err": (C.float() - ref).abs().max().item() / (0.02 * ref.abs().max().item() + 1e-3)}
+
+
+def test_rejected_call_keeps_ranks_in_step(lib):
+    world = _world()
+    for r in run_ranks(_rejected_call_worker, world, "nccl"):
+        assert r["raised"] and r["status"] == 0 and r["err"] <= 1.0, r

@@ -1,8 +1,8 @@
 """The allocation-free C entry point, called through its exported symbol.
 
-Some callers of this library cannot allocate device memory: code running inside a CUDA graph
-capture or an allocator callback, a process whose memory pool belongs entirely to a serving
-runtime, or a plain C host without PyTorch.  ``fo_fused_loopback_noalloc`` gives them the fused
+Some callers of this library cannot allocate device memory: code running inside another
+allocator's callback, a process whose device memory belongs entirely to a serving runtime's
+pool, or a plain C host without PyTorch.  ``fo_fused_loopback_noalloc`` gives them the fused
 GEMM+collective emulation with its scratch (staging buffers, arrival counters, status words) in
 a fixed array inside the library.  This test calls it twice in a row via ctypes and compares
 each result with the regular entry point (``torch.ops.flashoverlap_op.fused_loopback``), which
@@ -70,5 +70,10 @@ def test_noalloc_entry_rejects_oversize(cuda, lib):
     # 2 ranks x 4096 x 4096 x 2 B = 64 MiB of staging: beyond the 16 MiB built in
     rc, msg = _call(fn, 0, A, B, out, 4096, 4096, 64, 0, True)
     assert rc == -2 and "exceeds" in msg
-    rc, msg = _call(fn, 0, A, B, out, 128, 256, 64, 1, True)       # CTA-pair Algo is refused
+    rc, msg = _call(fn, 0, A, B, out, 128, 256, 64, 1, True)       # CTA-pair Algos are refused
     assert rc == -1 and "Algo" in msg
+    rc, msg = _call(fn, 0, A, B, out, 128, 256, 64, 3, True)
+    assert rc == -1 and "Algo" in msg
+    for bad in ((-128, -256, 64), (0, 256, 64), (128, 256, 0)):   # non-positive sizes never reach the size arithmetic
+        rc, msg = _call(fn, 0, A, B, out, *bad, 0, True)
+        assert rc == -1 and "positive" in msg, (bad, rc, msg)
