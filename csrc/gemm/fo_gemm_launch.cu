@@ -86,32 +86,37 @@ cudaError_t launch_one(const GemmTensorMaps* maps, const GemmParams* p, int grid
   return cudaLaunchKernelEx(&cfg, kernel, *maps, *p);
 }
 
+// One case per kernel of gemm/fo_gemm_instances.inc.
 template <bool BF16, bool FUSED, bool A2A = false, bool NORM = false, bool TRACE = false>
 cudaError_t launch_kernel_index(int kidx, const GemmTensorMaps* maps, const GemmParams* p,
                                 int grid_x, int nvr, bool coop, cudaStream_t s, int* query) {
   switch (kidx) {
-    case 0: return launch_one<256, 4, BF16, FUSED, false, 1, A2A, NORM, TRACE>(maps, p, grid_x, nvr, coop, s, query);
-    case 1: return launch_one<256, 6, BF16, FUSED, true, 1, A2A, NORM, TRACE>(maps, p, grid_x, nvr, coop, s, query);
-    case 2: return launch_one<128, 6, BF16, FUSED, false, 1, A2A, NORM, TRACE>(maps, p, grid_x, nvr, coop, s, query);
-    default: return launch_one<256, 4, BF16, FUSED, true, 2, A2A, NORM, TRACE>(maps, p, grid_x, nvr, coop, s, query);
+#define FO_GEMM_KERNEL(idx, bn, stages, cta2, mt, stages_epi4) \
+  case idx:                                                    \
+    return launch_one<bn, stages, BF16, FUSED, cta2, mt, A2A, NORM, TRACE>(maps, p, grid_x, nvr, coop, s, query);
+#include "fo_gemm_instances.inc"
+#undef FO_GEMM_KERNEL
+    default: return cudaErrorInvalidValue;
   }
 }
 
-// Fused kernels with four epilogue chunk buffers, paid for with one operand stage.
+// Fused kernels with four epilogue chunk buffers, paid for with operand stages.
 template <bool BF16>
 cudaError_t launch_epi4(int kidx, const GemmTensorMaps* maps, const GemmParams* p, int grid_x, int nvr,
                         bool coop, cudaStream_t s, int* query) {
   switch (kidx) {
-    case 0: return launch_one<256, 3, BF16, true, false, 1, false, false, false, 4>(maps, p, grid_x, nvr, coop, s, query);
-    case 1: return launch_one<256, 5, BF16, true, true, 1, false, false, false, 4>(maps, p, grid_x, nvr, coop, s, query);
-    case 2: return launch_one<128, 5, BF16, true, false, 1, false, false, false, 4>(maps, p, grid_x, nvr, coop, s, query);
-    default: return launch_one<256, 3, BF16, true, true, 2, false, false, false, 4>(maps, p, grid_x, nvr, coop, s, query);
+#define FO_GEMM_KERNEL(idx, bn, stages, cta2, mt, stages_epi4) \
+  case idx:                                                    \
+    return launch_one<bn, stages_epi4, BF16, true, cta2, mt, false, false, false, 4>(maps, p, grid_x, nvr, coop, s, query);
+#include "fo_gemm_instances.inc"
+#undef FO_GEMM_KERNEL
+    default: return cudaErrorInvalidValue;
   }
 }
 
 cudaError_t dispatch(int algo, bool bf16, bool fused, const GemmTensorMaps* maps, const GemmParams* p,
                      int grid_x, int nvr, bool coop, cudaStream_t s, int* query) {
-  const int kidx = algo & 3;
+  const int kidx = algo_kernel(algo);
   if (fused && p != nullptr && p->epi_bufs == 4 && p->norm_w == nullptr && p->trace == nullptr) {
     return bf16 ? launch_epi4<true>(kidx, maps, p, grid_x, nvr, coop, s, query)
                 : launch_epi4<false>(kidx, maps, p, grid_x, nvr, coop, s, query);
@@ -188,20 +193,21 @@ void set_l2_hints(GemmParams* p, bool enable) {
 }
 
 int gemm_smem_bytes(int algo) {
-  switch (algo & 3) {
-    case 0: return GemmSmem<256, 4, false>::kTotalBytes;
-    case 1: return GemmSmem<256, 6, true>::kTotalBytes;
-    case 2: return GemmSmem<128, 6, false>::kTotalBytes;
-    default: return GemmSmem<256, 4, true, 2>::kTotalBytes;
+  switch (algo_kernel(algo)) {
+#define FO_GEMM_KERNEL(idx, bn, stages, cta2, mt, stages_epi4) \
+  case idx: return GemmSmem<bn, stages, cta2, mt>::kTotalBytes;
+#include "fo_gemm_instances.inc"
+#undef FO_GEMM_KERNEL
+    default: return 0;
   }
 }
 
 int gemm_max_resident_ctas(int algo, bool bf16, bool fused) {
-  static int cache[16][4][2][2] = {};
+  static int cache[16][kNumKernels][2][2] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 16) dev = 0;
-  int& slot = cache[dev][algo & 3][bf16 ? 1 : 0][fused ? 1 : 0];
+  int& slot = cache[dev][algo_kernel(algo)][bf16 ? 1 : 0][fused ? 1 : 0];
   if (slot == 0) {
     int q = 0;
     if (dispatch(algo, bf16, fused, nullptr, nullptr, 0, 1, false, nullptr, &q) != cudaSuccess || q <= 0) {

@@ -83,6 +83,10 @@ struct GemmParams {
   // with one peer load per rank.
   int stage_local;
   void* mc_stage;
+  // Pull variant only: 1 = the epilogue threads store the partial tile into the local staging
+  // themselves (16-byte stores, as the plain kernels do) and the push warp only announces it;
+  // 0 = every chunk is handed to the push warp, which stores it with TMA.
+  int pull_direct;
   // All-to-all kernels: [virtual rank][2][kMaxRanks] ints on the device.  Row 0: end (exclusive)
   // of the run of C rows bound for each rank, runs packed in rank order; row 1: the row of that
   // rank's receive buffer where this rank's run starts.  C rows past the last run go nowhere.
@@ -123,6 +127,11 @@ enum TraceSlot : int {
 };
 
 // ------------------------------------------------------------------ Algo table
+//
+// Kernels (tile configurations that are template instantiations) and Algos ((kernel, raster
+// strip) pairs) come from gemm/fo_gemm_instances.inc, which tool/generate_instances.py writes
+// from tool/instances.json.  Adding a kernel or a raster there appends Algo numbers; existing
+// numbers never change.
 
 struct AlgoConfig {
   int bm, bn, bk;
@@ -130,26 +139,47 @@ struct AlgoConfig {
   int raster_sw;  // 0 => full row panels (strip = all N tiles)
   int cta2;       // 1: CTA pairs share 256-row tiles through tcgen05.mma.cta_group::2
   int mt;         // 128-row halves per CTA (2: a pair covers 512 x 256, accumulators fill TMEM)
+  int kernel;     // index of the kernel (template instantiation set) this Algo runs
 };
 
-constexpr int kNumAlgos = 24;
+struct KernelEntry {
+  int bn, stages, cta2, mt, stages_epi4;
+};
+struct AlgoEntry {
+  int kernel, raster_sw;
+};
+
+constexpr KernelEntry kKernelTable[] = {
+#define FO_GEMM_KERNEL(idx, bn, stages, cta2, mt, stages_epi4) {bn, stages, (cta2) ? 1 : 0, mt, stages_epi4},
+#include "fo_gemm_instances.inc"
+#undef FO_GEMM_KERNEL
+};
+constexpr AlgoEntry kAlgoTable[] = {
+#define FO_GEMM_ALGO(algo, kernel, raster) {kernel, raster},
+#include "fo_gemm_instances.inc"
+#undef FO_GEMM_ALGO
+};
+constexpr int kNumKernels = static_cast<int>(sizeof(kKernelTable) / sizeof(kKernelTable[0]));
+constexpr int kNumAlgos = static_cast<int>(sizeof(kAlgoTable) / sizeof(kAlgoTable[0]));
+
+inline int algo_kernel(int algo) {
+  if (algo < 0 || algo >= kNumAlgos) algo = 0;
+  return kAlgoTable[algo].kernel;
+}
 
 inline AlgoConfig algo_config(int algo) {
-  // algo = raster index * 4 + kernel index
-  static const int kKernelBN[4] = {256, 256, 128, 256};
-  static const int kKernelStages[4] = {4, 6, 6, 4};
-  static const int kKernelCta2[4] = {0, 1, 0, 1};
-  static const int kKernelMt[4] = {1, 1, 1, 2};
-  static const int kRaster[6] = {8, 4, 2, 1, 16, 0};
   if (algo < 0 || algo >= kNumAlgos) algo = 0;
+  const AlgoEntry a = kAlgoTable[algo];
+  const KernelEntry k = kKernelTable[a.kernel];
   AlgoConfig c;
   c.bm = kBM;
   c.bk = kBK;
-  c.bn = kKernelBN[algo & 3];
-  c.stages = kKernelStages[algo & 3];
-  c.raster_sw = kRaster[algo >> 2];
-  c.cta2 = kKernelCta2[algo & 3];
-  c.mt = kKernelMt[algo & 3];
+  c.bn = k.bn;
+  c.stages = k.stages;
+  c.raster_sw = a.raster_sw;
+  c.cta2 = k.cta2;
+  c.mt = k.mt;
+  c.kernel = a.kernel;
   return c;
 }
 

@@ -374,7 +374,9 @@ __device__ __forceinline__ void reduce_tile_pull(const GemmParams& p, int me, in
   const bool sw_reduce = p.mc_stage != nullptr;
   constexpr int U = (16 / WS) < 1 ? 1 : (16 / WS);  // vectors per thread per round (peer loads)
   // vectors per thread per round (switch reduction)
-  constexpr int UM = (kTotalVec / kReducerThreads) >= 4 ? 4 : (kTotalVec / kReducerThreads);
+  // (8 x 16 B per thread = 16 KB per CTA in flight: a switch-side reduction takes several
+  // microseconds to answer, and only requests in flight keep the links busy)
+  constexpr int UM = (kTotalVec / kReducerThreads) >= 8 ? 8 : ((kTotalVec / kReducerThreads) >= 4 ? 4 : (kTotalVec / kReducerThreads));
   static_assert(kTotalVec % (kReducerThreads * U) == 0 && kTotalVec % (kReducerThreads * UM) == 0,
                 "tile slice must split evenly over the reducer threads");
 
@@ -714,6 +716,11 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
     // (row-major and tile-contiguous layouts); the row-scatter and all-to-all modes, whose rows
     // go to unrelated addresses, keep the per-thread 16-byte stores.
     const bool use_tma = !FUSED && !A2A && p.tma_out != 0;
+    // Fused kernels, pull protocol with direct stores: the partial tile goes to this rank's own
+    // staging buffer, so the epilogue threads can store it themselves (as the plain kernels do)
+    // instead of handing every chunk to the push warp for a TMA store; the push warp then only
+    // announces the finished tile.  chunk_ready / chunk_free count tiles in this mode.
+    const bool direct = FUSED && p.stage_local != 0 && p.pull_direct != 0;
 
     bool go = true;
     if constexpr (A2A) {
@@ -847,8 +854,8 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
           // The buffer is free once the push warp's stores of its previous use have read it.
           // A failed wait raises the abort flag but the thread stays in step with the others:
           // everybody leaves together at the next tile boundary.
-          if (!ptx::mbar_wait_bounded(&chunk_free_bar[chunk_no % EPI], ((chunk_no / EPI) & 1u) ^ 1u, s_abort,
-                                      pipe_timeout)) {
+          if (!direct && !ptx::mbar_wait_bounded(&chunk_free_bar[chunk_no % EPI], ((chunk_no / EPI) & 1u) ^ 1u,
+                                                 s_abort, pipe_timeout)) {
             *s_abort = 1;
           }
         }
@@ -859,7 +866,7 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
             ptx::named_bar_sync(1, kEpilogueThreads);
           }
         }
-        const int bsel = FUSED ? static_cast<int>(chunk_no % EPI) : (c & 1);
+        const int bsel = (FUSED && !direct) ? static_cast<int>(chunk_no % EPI) : (c & 1);
         uint8_t* buf = epi + bsel * L::kEpiBufBytes + smem_row * 128;
         const int sw = smem_row & 7;
 #pragma unroll
@@ -881,10 +888,25 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
           *reinterpret_cast<uint4*>(buf + (((j + 4) ^ sw) * 16)) = w;
         }
         if constexpr (FUSED) {
-          // Hand the chunk to the push warp (generic-proxy writes ordered before its TMA reads).
-          ptx::fence_proxy_async_smem();
-          ptx::mbar_arrive(&chunk_ready_bar[chunk_no % EPI]);
-          ++chunk_no;
+          if (direct) {
+            // rows are grouped by owner in shared memory exactly as in the staging layout
+            // [tile][owner][rows owned][BN]: shared row lr is staging row t * 128 + lr
+            ptx::named_bar_sync(1, kEpilogueThreads);
+            const uint8_t* rbuf = epi + (c & 1) * L::kEpiBufBytes;
+            uint8_t* srow = reinterpret_cast<uint8_t*>(p.stage[me]) +
+                            ((static_cast<size_t>(t) * kBM + (et >> 3)) * BN + c * 64) * 2 + (et & 7) * 16;
+#pragma unroll
+            for (int i = 0; i < 8 && !(p.diag & 2); ++i) {
+              const int lr = (et >> 3) + 16 * i;
+              const uint4 w = *reinterpret_cast<const uint4*>(rbuf + lr * 128 + (((et & 7) ^ (lr & 7)) * 16));
+              ptx::st_v4(srow + static_cast<size_t>(16 * i) * BN * 2, w);
+            }
+          } else {
+            // Hand the chunk to the push warp (generic-proxy writes ordered before its TMA reads).
+            ptx::fence_proxy_async_smem();
+            ptx::mbar_arrive(&chunk_ready_bar[chunk_no % EPI]);
+            ++chunk_no;
+          }
         } else if (use_tma) {
           ptx::fence_proxy_async_smem();  // generic-proxy writes before the async-proxy read
           ptx::named_bar_sync(1, kEpilogueThreads);
@@ -908,6 +930,17 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
       if constexpr (FUSED) {
         // arrival counters are bumped by the push warp
         if (et == 0) stamp(t, kTraceEpilogueDone);
+        if (direct) {
+          // The tile's stores have been issued by this thread: hand the tile to the push warp
+          // (release at CTA scope; its system-scope fence then covers these stores).  The slot
+          // is free once the push warp has announced the tile that used it EPI tiles ago.
+          if (!ptx::mbar_wait_bounded(&chunk_free_bar[chunk_no % EPI], ((chunk_no / EPI) & 1u) ^ 1u, s_abort,
+                                      pipe_timeout)) {
+            *s_abort = 1;
+          }
+          ptx::mbar_arrive(&chunk_ready_bar[chunk_no % EPI]);
+          ++chunk_no;
+        }
       } else {
         // All of this tile's stores have been issued by every epilogue thread.
         if (!use_tma) ptx::named_bar_sync(1, kEpilogueThreads);
@@ -1143,6 +1176,24 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
           const int t = tc.m * p.tiles_n + tc.n;
           const int r = tile_position(p, t, status);
           const int row0 = (me * p.num_tiles + t) * rows_owned;
+          if (p.stage_local != 0 && p.pull_direct != 0) {
+            // The epilogue threads stored the tile into the local staging themselves; announce it.
+            const int b = static_cast<int>(chunk_no % EPI);
+            if (!ptx::mbar_wait_bounded(&chunk_ready_bar[b], (chunk_no / EPI) & 1u, s_abort, pipe_timeout)) {
+              ptx::report_status(status, kStatusTimeoutTmemFull, pos, 0, 2);
+              *s_abort = 1;
+              ok = false;
+              break;
+            }
+            stamp(t, kTracePushIssued);
+            int g, need;
+            group_of_position(p, r, &g, &need);
+            signal_group(g);
+            stamp(t, kTraceSignalled);
+            ptx::mbar_arrive(&chunk_free_bar[b]);
+            ++chunk_no;
+            continue;
+          }
           for (int c = 0; c < kChunks; ++c, ++chunk_no) {
             const int b = static_cast<int>(chunk_no % EPI);
             if (!ptx::mbar_wait_bounded(&chunk_ready_bar[b], (chunk_no / EPI) & 1u, s_abort, pipe_timeout)) {

@@ -17,7 +17,7 @@ std::vector<int64_t> fused_loopback(std::string comm_op, std::vector<at::Tensor>
                                     int64_t timeout_ms, bool stage_local,
                                     c10::optional<at::Tensor> mlen_opt,
                                     c10::optional<at::Tensor> norm_w, double norm_eps,
-                                    c10::optional<at::Tensor> trace, int64_t epi_bufs) {
+                                    c10::optional<at::Tensor> trace, int64_t epi_bufs, int64_t pull_direct) {
   const at::Tensor RA = RA_opt.has_value() ? *RA_opt : at::Tensor();
   const at::Tensor cseg_gpu = cseg_opt.has_value() ? *cseg_opt : at::Tensor();
   const int ws = static_cast<int>(A.size());
@@ -44,7 +44,7 @@ std::vector<int64_t> fused_loopback(std::string comm_op, std::vector<at::Tensor>
   cuda_check(cudaGetDeviceProperties(&prop, dev), "cudaGetDeviceProperties");
 
   FO_CHECK(!algo_config(static_cast<int>(algo)).cta2,
-           "the loopback emulation runs single-CTA Algos only (Algo & 3 != 1)");
+           "the loopback emulation runs single-CTA Algos only (no CTA-pair kernels)");
   GemmTensorMaps maps;
   GemmParams p;
   std::memset(&p, 0, sizeof(p));
@@ -97,6 +97,7 @@ std::vector<int64_t> fused_loopback(std::string comm_op, std::vector<at::Tensor>
   p.strided_rows = strided_rows ? 1 : 0;
   p.push_lag = default_push_lag(p.K);
   p.stage_local = stage_local ? 1 : 0;
+  p.pull_direct = (stage_local && pull_direct != 0) ? 1 : 0;
   FO_CHECK(epi_bufs == 2 || epi_bufs == 4, "epi_bufs must be 2 or 4");
   p.epi_bufs = static_cast<int>(epi_bufs);
   if (a2a) {

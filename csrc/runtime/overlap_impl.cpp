@@ -102,6 +102,9 @@ void OverlapImpl::SetOption(std::string name, int64_t value) {
   } else if (name == "diag") {
     FO_CHECK(value >= 0 && value <= 7, "diag is a bit mask of 1 | 2 | 4");
     opt_diag_ = value;
+  } else if (name == "pull_direct") {
+    FO_CHECK(value >= -1 && value <= 1, "pull_direct must be -1 (automatic), 0 or 1");
+    opt_pull_direct_ = value;
   } else if (name == "validate") {
     opt_validate_ = value ? 1 : 0;
   } else if (name == "tma_out") {
@@ -127,6 +130,7 @@ int64_t OverlapImpl::GetOption(std::string name) {
   if (name == "epi_bufs") return opt_epi_bufs_;
   if (name == "tma_out") return opt_tma_out_;
   if (name == "validate") return opt_validate_;
+  if (name == "pull_direct") return opt_pull_direct_;
   if (name == "diag") return opt_diag_;
   if (name == "sm_count") return sm_count_;
   if (name == "rank") return rank_;
@@ -510,6 +514,9 @@ void OverlapImpl::run_fused(int comm, const at::Tensor& A, const at::Tensor& B, 
   const SymmetricRegion* stage =
       (pull && user_stage_ != nullptr && user_stage_->bytes >= full_bytes) ? user_stage_ : stage_;
   p.stage_local = pull ? 1 : 0;
+  // Direct stores pay where the epilogue is exposed (the 256 x 256-per-CTA kernels, whose
+  // accumulators fill TMEM); elsewhere the TMA hand-over costs fewer issue slots.
+  p.pull_direct = (pull && (opt_pull_direct_ > 0 || (opt_pull_direct_ < 0 && algo_config(algo).mt == 2))) ? 1 : 0;
   p.epi_bufs = static_cast<int>(opt_epi_bufs_);
   p.diag = static_cast<int>(opt_diag_);
   if (pull && stage->multicast != nullptr && opt_nvls_ != 0) p.mc_stage = stage->multicast;

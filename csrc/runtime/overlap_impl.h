@@ -75,6 +75,9 @@ class OverlapImpl : public torch::CustomClassHolder {
   // "push_lag" (tiles of pushes kept in flight before their arrival is signalled; 0 = from K),
   // "stage_local" (1: pull protocol - partials stay in the producing rank's staging buffer and
   // the owners fetch them, through the switch's reduction when the buffer has a multicast mapping),
+  // "pull_direct" (pull protocol only; 1: the epilogue threads store the partial tile into the
+  // local staging themselves and the push warp only announces it, 0: chunks go through the push
+  // warp's TMA stores, -1, the default: direct for the 256 x 256-per-CTA kernels),
   // "epi_bufs" (2 | 4: fused kernels with four epilogue chunk buffers and one operand stage fewer;
   // their push warp keeps three chunks of stores in flight instead of waiting for each),
   // "validate" (1: overlap calls also check the values of RA / RE / cSEG_GPU - permutation, range,
@@ -184,6 +187,7 @@ class OverlapImpl : public torch::CustomClassHolder {
   int64_t opt_validate_ = 0;     // 1: also check the VALUES of RA / RE / cSEG_GPU (a device-to-host copy per call)
 #endif
   int64_t opt_tma_out_ = -1;     // plain kernels' stores: 1 TMA tensor stores, 0 per-thread stores, -1 by kernel
+  int64_t opt_pull_direct_ = -1;  // pull protocol: epilogue threads store the partials themselves (1), TMA (0), by kernel (-1)
   int64_t opt_stage_local_ = 0;  // 1: pull protocol (partials staged locally, owners fetch them)
   int64_t opt_l2_hints_ = 0;  // measured: priorities raise DRAM traffic on B200, off by default
 };

@@ -75,7 +75,7 @@ def fused_loopback(comm_op: str, A: List[torch.Tensor], B: List[torch.Tensor], o
                    timeout_ms: int = 1000, stage_local: bool = False,
                    mlen: Optional[torch.Tensor] = None, norm_w: Optional[torch.Tensor] = None,
                    norm_eps: float = 1e-5, trace: Optional[torch.Tensor] = None,
-                   epi_bufs: int = 2) -> List[List[int]]:
+                   epi_bufs: int = 2, pull_direct: bool = False) -> List[List[int]]:
     """All ranks of a fused GEMM+collective on ONE GPU in one cooperative launch (test aid).
 
     ``stage_local`` selects the pull protocol: every rank stages its partial tiles in its own
@@ -85,7 +85,9 @@ def fused_loopback(comm_op: str, A: List[torch.Tensor], B: List[torch.Tensor], o
     ``out[r]``; ``mlen`` is the int32 host matrix of row counts [ranks, ranks].  ``norm_w`` (with
     ``comm_op="reduce_scatter"`` and ``natural_out``) turns on the RMSNorm tail of the reducers.
     ``trace`` (int64 CUDA tensor, ranks * tiles * 8) receives the per-tile timeline, see
-    ``flashoverlap_b200.utils.trace``.  ``epi_bufs=4`` runs the build with four epilogue chunk buffers."""
+    ``flashoverlap_b200.utils.trace``.  ``epi_bufs=4`` runs the build with four epilogue chunk buffers.
+    ``pull_direct`` (with ``stage_local``): the epilogue threads store the partial tiles into the local
+    staging themselves instead of handing every chunk to the push warp's TMA stores."""
     flat = list(_op().fused_loopback(comm_op, A, B, out, RA, cseg, algo, strided_rows, natural_out, repeat,
-                                     timeout_ms, stage_local, mlen, norm_w, norm_eps, trace, epi_bufs))
+                                     timeout_ms, stage_local, mlen, norm_w, norm_eps, trace, epi_bufs, int(pull_direct)))
     return [flat[i:i + 8] for i in range(0, len(flat), 8)]

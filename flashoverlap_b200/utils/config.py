@@ -18,23 +18,41 @@ from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
 
-# (BN, stages, CTA pair, row halves per CTA) of the four kernels and the raster strips;
-# Algo = raster * 4 + kernel.
-# Must match algo_config() in csrc/gemm/fo_gemm_params.h (checked against the native table by
-# tests/test_config.py whenever the library is loaded).
-_KERNELS = [(256, 4, 0, 1), (256, 6, 1, 1), (128, 6, 0, 1), (256, 4, 1, 2)]
-_RASTERS = [8, 4, 2, 1, 16, 0]
-NUM_ALGOS = len(_KERNELS) * len(_RASTERS)
+# Kernels, raster strips and the Algo list come from the generated table (tool/generate_instances.py
+# writes it together with csrc/gemm/fo_gemm_instances.inc; tests/test_config.py checks it against
+# the native table whenever the library is loaded).
+from ._instances import ALGOS as _ALGOS, KERNELS as _KERNELS_FULL, RASTERS as _RASTERS
+
+_KERNELS = [k[:4] for k in _KERNELS_FULL]      # (BN, stages, CTA pair, row halves per CTA)
+NUM_KERNELS = len(_KERNELS)
+NUM_ALGOS = len(_ALGOS)
 BM = 128
 BK = 64
+
+
+def algo_kernel(algo: int) -> int:
+    """Index of the kernel (tile configuration) an Algo runs."""
+    if not 0 <= algo < NUM_ALGOS:
+        raise ValueError(f"Algo {algo} out of range [0, {NUM_ALGOS})")
+    return _ALGOS[algo][0]
+
+
+def algo_with_kernel(algo: int, kernel: int) -> int:
+    """The Algo that runs ``kernel`` with the raster of ``algo``."""
+    r = _ALGOS[algo][1]
+    for a, (k, rr) in enumerate(_ALGOS):
+        if k == kernel and rr == r:
+            return a
+    raise ValueError(f"no Algo for kernel {kernel} with raster {_RASTERS[r]}")
 
 
 def algo_params(algo: int) -> Dict[str, int]:
     if not 0 <= algo < NUM_ALGOS:
         raise ValueError(f"Algo {algo} out of range [0, {NUM_ALGOS})")
-    bn, stages, cta2, mt = _KERNELS[algo & 3]
-    return {"BM": BM, "BN": bn, "BK": BK, "stages": stages, "raster": _RASTERS[algo >> 2], "cta2": cta2, "mt": mt,
-            "rows_per_unit": (2 if cta2 else 1) * mt}
+    k, r = _ALGOS[algo]
+    bn, stages, cta2, mt = _KERNELS[k]
+    return {"BM": BM, "BN": bn, "BK": BK, "stages": stages, "raster": _RASTERS[r], "cta2": cta2, "mt": mt,
+            "rows_per_unit": (2 if cta2 else 1) * mt, "kernel": k}
 
 
 def algo_tuple(algo: int) -> Tuple[int, ...]:
@@ -141,12 +159,18 @@ def default_solution(M: int, N: int, algo: int = 0, wave_size: int = 148, groups
     """A usable config without any tuning run: analytic hint and one wave per group."""
     from . import layout
     p = algo_params(algo)
-    if N % p["BN"]:
-        algo = (algo & ~3) | 2
-        p = algo_params(algo)
-    if M % (p["rows_per_unit"] * p["BM"]):
-        algo = (algo & ~3) | (1 if M % (2 * p["BM"]) == 0 and N % 256 == 0 else (0 if N % 256 == 0 else 2))
-        p = algo_params(algo)
+
+    def fits(k):
+        bn, _, cta2, mt = _KERNELS[k]
+        return N % bn == 0 and M % ((2 if cta2 else 1) * mt * BM) == 0
+
+    if not fits(p["kernel"]):
+        # nearest kernel that divides the shape: CTA pairs, then one CTA per 128 x 256 tile, then BN = 128
+        for k in (1, 0, 2):
+            if fits(k):
+                algo = algo_with_kernel(algo, k)
+                p = algo_params(algo)
+                break
     tiles = (M // p["BM"]) * (N // p["BN"])
     hint = layout.analytic_hint(M, N, p["BM"], p["BN"], p["raster"], p["rows_per_unit"])
     nw = layout.div_up(tiles, wave_size)

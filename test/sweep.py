@@ -74,6 +74,25 @@ def worker(rank, world, args):
                            "speedup": round(base_ms / fused_ms, 4), "roofline_ms": round(roof, 5),
                            "roofline_frac": round(roof / fused_ms, 4)}
                     if args.groupings and world > 1:
+                        # fused mechanism: wave groups only coarsen the arrival counters; the search
+                        # space is the same compositions plus one counter per tile
+                        grid = min(sm * config.algo_params(algo)["mt"], wl.tiles)
+                        f_cands = tuner.candidate_groupings(wl.tiles, grid, max_waves_per_unit=4) + [[1] * wl.tiles]
+
+                        def measure_fused(cseg):
+                            wl.set_cseg(cseg)
+                            return perf_ms(wl.run, 3, max(5, args.reps // 2), args.flush)
+
+                        cs_e, t_e, _ = tuner.exhaustive_search(f_cands, measure_fused)
+                        rec.update(fused_best_groups=len(cs_e), fused_best_ms=round(t_e, 5))
+                        f_curve = config.bandwidth_path(comm_op, world, args.path).parent / f"bandwidth_fused_{comm_op}_tp{world}.pt"
+                        if os.path.exists(f_curve):
+                            prob = tuner.Problem(M, N, wl.BM, wl.BN, gemm_ms, sm, world, comm_op, grid=grid)
+                            cs_p, t_p = tuner.predictive_search(prob, torch.load(f_curve), "fused", f_cands, grid)
+                            t_pm = measure_fused(cs_p)
+                            rec.update(fused_predicted_groups=len(cs_p), fused_predicted_model_ms=round(t_p, 5),
+                                       fused_predicted_measured_ms=round(t_pm, 5),
+                                       fused_pick_within=round(t_pm / t_e, 4), fused_model_error=round(t_p / t_pm - 1.0, 4))
                         curve_path = config.bandwidth_path(comm_op, world, args.path)
                         wave = sm - margin
                         wl.mode = "gated"
@@ -84,13 +103,16 @@ def worker(rank, world, args):
                             wl.set_cseg(cseg)
                             return perf_ms(wl.run, 3, max(5, args.reps // 4))
 
+                        wl.mode = "gated"
                         cs_e, t_e, _ = tuner.exhaustive_search(cands, measure)
                         rec.update(gated_best_cseg=cs_e, gated_best_ms=round(t_e, 5))
                         if os.path.exists(curve_path):
                             prob = tuner.Problem(M, N, wl.BM, wl.BN, gemm_ms, sm, world, comm_op, sm_margin=margin)
                             cs_p, t_p = tuner.predictive_search(prob, torch.load(curve_path), "gated", cands, wave)
+                            t_pm = measure(cs_p)
                             rec.update(gated_predicted_cseg=cs_p, gated_predicted_model_ms=round(t_p, 5),
-                                       gated_predicted_measured_ms=round(measure(cs_p), 5))
+                                       gated_predicted_measured_ms=round(t_pm, 5), gated_pick_within=round(t_pm / t_e, 4),
+                                       gated_model_error=round(t_p / t_pm - 1.0, 4))
                     impl.check_status()
                     torch.cuda.synchronize()
                     if world > 1:

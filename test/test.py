@@ -78,7 +78,11 @@ def worker(rank, world, args):
         res["fused_pull_peer_ms"] = perf_ms(checked(wl.run), WARM_UP, args.reps, f)
         _, switch = symm.alloc_stage(impl, args.m, args.n, dt)
         if switch:
-            res["fused_pull_switch_ms"] = perf_ms(checked(wl.run), WARM_UP, args.reps, f)
+            for direct in (0, 1):
+                impl.set_option("pull_direct", direct)
+                res["fused_pull_switch_direct_ms" if direct else "fused_pull_switch_ms"] = \
+                    perf_ms(checked(wl.run), WARM_UP, args.reps, f)
+            impl.set_option("pull_direct", -1)
         impl.set_option("stage_local", 0)
     if world > 1 and args.epi4:
         impl.set_option("epi_bufs", 4)
@@ -116,6 +120,7 @@ def worker(rank, world, args):
         print(f"{'overlap (fused)':>24} {res['fused_ms']:.4f} ms   speedup {res['speedup_fused']:.3f}   "
               f"roofline {res['roofline_ms']:.4f} ms ({100 * res['roofline_frac']:.1f}% of measured peaks)")
         for key, label in (("fused_pull_peer_ms", "fused, pull (peer loads)"), ("fused_pull_switch_ms", "fused, pull (switch sum)"),
+                           ("fused_pull_switch_direct_ms", "pull (switch), direct st"),
                            ("fused_epi4_ms", "fused, 4 chunk buffers")):
             if key in res:
                 print(f"{label:>24} {res[key]:.4f} ms   speedup {res['baseline_ms'] / res[key]:.3f}")

@@ -40,11 +40,11 @@ def test_default_solution_is_consistent():
     tiles = (1024 // c["BM"]) * (2048 // c["BN"])
     assert sorted(c["hint"]) == list(range(tiles)) and sum(c["cSeg"]) == tiles
     c = config.default_solution(1024, 2048 + 128, algo=0)      # N not a multiple of 256 -> BN 128
-    assert c["BN"] == 128 and (c["Algo"] & 3) == 2
+    assert c["BN"] == 128 and config.algo_kernel(c["Algo"]) == 2
     c = config.default_solution(768, 2048, algo=3)             # M not a multiple of 512 -> plain CTA pairs
-    assert (c["Algo"] & 3) == 1 and sorted(c["hint"]) == list(range((768 // 128) * (2048 // 256)))
+    assert config.algo_kernel(c["Algo"]) == 1 and sorted(c["hint"]) == list(range((768 // 128) * (2048 // 256)))
     c = config.default_solution(1024, 2048, algo=7)            # two halves per CTA: units of 4 tile rows
-    assert (c["Algo"] & 3) == 3 and c["hint"][:4] == [0, 8, 16, 24]
+    assert config.algo_kernel(c["Algo"]) == 3 and c["hint"][:4] == [0, 8, 16, 24]
 
 
 def test_gen_config_csv_rows_map_back_to_algos(tmp_path, monkeypatch):

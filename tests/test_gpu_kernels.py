@@ -74,7 +74,8 @@ def test_reference_signature_reorder_rmsnorm(cuda):
                                         (256, 256, 64, 1), (2048, 4096, 1024, 5), (4096, 2048, 512, 9),
                                         (8192, 8192, 256, 17), (1536, 1280, 384, 21),
                                         (512, 512, 64, 3), (2048, 2048, 1024, 7), (4096, 8192, 512, 19),
-                                        (1024, 768, 320, 23)])
+                                        (1024, 768, 320, 23), (512, 256, 192, 24), (2048, 4096, 512, 26),
+                                        (4096, 2048, 1024, 29)])
 def test_gemm_natural(cuda, impl, dt, M, N, K, algo):
     a, b = _rand((M, K), dt, cuda), _rand((N, K), dt, cuda)
     c = torch.full((M, N), float("nan"), device=cuda, dtype=dt)
@@ -420,7 +421,7 @@ def test_check_status_raises_with_decoded_message(cuda):
         i.wait_flag(1, mm, 9)
 
 
-@pytest.mark.parametrize("algo", [0, 1, 2, 3, 22])
+@pytest.mark.parametrize("algo", [0, 1, 2, 3, 22, 25])
 def test_plain_epilogues_agree(cuda, algo):
     """TMA tensor stores and per-thread stores must write the same bytes, in the row-major and the
     tile-contiguous layout (rLDN 1 and 2)."""
@@ -451,3 +452,25 @@ def test_plain_epilogues_agree(cuda, algo):
     i.check_status()
     for key in ("nat", 1, 2):
         assert torch.equal(outs[(key, 1)], outs[(key, 0)]), key
+
+
+@pytest.mark.parametrize("comm_op", ["all_reduce", "reduce_scatter"])
+@pytest.mark.parametrize("ws,algo,strided", [(2, 0, True), (4, 2, False), (8, 0, True)])
+def test_fused_loopback_pull_direct_stores(cuda, comm_op, ws, algo, strided):
+    """Pull protocol whose epilogue threads store the partial tiles into the local staging
+    themselves (the push warp only announces each tile); repeated calls reuse the staging."""
+    M, N, K = 1024, 1024, 192
+    A = [_rand((M, K), torch.bfloat16, cuda) for _ in range(ws)]
+    B = [_rand((N, K), torch.bfloat16, cuda) for _ in range(ws)]
+    full = sum(a.float() @ b.float().t() for a, b in zip(A, B))
+    rows = M if comm_op == "all_reduce" else M // ws
+    out = [torch.full((rows, N), float("nan"), device=cuda, dtype=torch.bfloat16) for _ in range(ws)]
+    st = ops.fused_loopback(comm_op, A, B, out, algo=algo, strided_rows=strided, natural_out=True, repeat=3,
+                            stage_local=True, pull_direct=True)
+    assert all(s[0] == 0 for s in st), st
+    for r in range(ws):
+        if comm_op == "all_reduce":
+            ref = full
+        else:
+            ref = full[layout.owned_rows(M, 128, ws, r, strided).to(cuda)]
+        assert (out[r].float() - ref).abs().max().item() <= _tol(full), (comm_op, r)
