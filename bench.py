@@ -116,7 +116,7 @@ class ClockSampler:
         return out
 
 
-def pick_algo(torch, dist, world, run, candidates, flush, reps=10, settle_seconds=WARM_SECONDS):
+def pick_algo(torch, dist, world, run, candidates, flush, reps=10, settle_seconds=WARM_SECONDS, check=None):
     """Fastest Algo by a short timing, agreed on by all ranks (max over ranks per candidate).
     The candidates are ranked in the regime of the timed region: after the same settling time
     under load (a cold GPU runs all of them at boost clocks, while the timed region runs at the
@@ -140,7 +140,14 @@ def pick_algo(torch, dist, world, run, candidates, flush, reps=10, settle_second
     times = []
     for a in candidates:
         try:
-            for _ in range(3):
+            run(a)
+            if check is not None:
+                # a candidate whose device-side waits give up is dropped after ONE call instead of
+                # running into its time limit on every timed iteration
+                torch.cuda.synchronize()
+                if not check():
+                    raise RuntimeError("device status not ok")
+            for _ in range(2):
                 run(a)
                 flush()
             ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(reps)]
@@ -301,7 +308,7 @@ def run_ours(args):
     torch.manual_seed(1234 + rank)
     flush = make_flusher(torch)
     impl = bootstrap.make_overlap_impl(rank, world)
-    impl.set_option("timeout_ms", 20000)
+    impl.set_option("timeout_ms", 3000)
 
     M, N, K = M_AR, N_AR, K_AR_TOTAL // world
     A = (torch.randn(M, K, device=dev) * 0.02).to(torch.bfloat16)
@@ -320,6 +327,17 @@ def run_ours(args):
             protocols = ["pull"] if args.protocol == "pull" else ["push", "pull"]
         except Exception:
             protocols = ["push"]
+
+    def healthy():
+        """True when no rank's device-side wait has given up; otherwise all ranks re-align their
+        call counters (collective) and the caller drops whatever it was trying."""
+        ok = torch.tensor([1 if impl.read_status()[0] == 0 else 0], device=dev, dtype=torch.int32)
+        if world > 1:
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if int(ok.item()) == 1:
+            return True
+        impl.resync()
+        return False
 
     state = {}
 
@@ -352,7 +370,7 @@ def run_ours(args):
             cand = (cand[0], protocols[-1])
     else:
         cands = [(a, pr) for pr in protocols for a in ((19, 3, 17, 1) if world <= 2 else (3, 1, 19, 17))]
-        cand, algo_times = pick_algo(torch, dist, world, step_cand, cands, flush)
+        cand, algo_times = pick_algo(torch, dist, world, step_cand, cands, flush, check=healthy)
     algo, protocol = cand
 
     sampler = ClockSampler(local) if rank == 0 else None
@@ -410,7 +428,7 @@ def run_ours(args):
     if not args.no_extra:
         try:
             extra.update(extras(torch, dist, impl, rank, world, dev, A, B, C, algo, flush, peaks, args.steps, protocol,
-                                protocols, args.no_nvls))
+                                protocols, args.no_nvls, healthy))
             extra.update(reference_ratios(world, ms, extra))
         except Exception as ex:  # extras never block the headline line
             extra["extras_error"] = repr(ex)[:300]
@@ -438,7 +456,7 @@ def run_ours(args):
 
 
 def extras(torch, dist, impl, rank, world, dev, A, B, C, algo, flush, peaks, steps_main, protocol="push",
-           protocols=("push",), no_nvls=False):
+           protocols=("push",), no_nvls=False, healthy=None):
     """Comparison arms on the same box: our GEMM then one NCCL call (non-overlap), cuBLAS + NCCL,
     the counter-gated NCCL mechanism, and the GEMM+ReduceScatter+RMSNorm config."""
     from flashoverlap_b200 import ops
@@ -532,7 +550,7 @@ def extras(torch, dist, impl, rank, world, dev, A, B, C, algo, flush, peaks, ste
     rs_cands = [(a, pr, "norm_kernel") for pr in rs_protocols for a in (0, 1, 3)]
     if world > 1:
         rs_cands += [(a, "push", "tail") for a in (0, 1)]
-    rs_cand, rs_probe = pick_algo(torch, dist, world, rs_step, rs_cands, flush, settle_seconds=0.3)
+    rs_cand, rs_probe = pick_algo(torch, dist, world, rs_step, rs_cands, flush, settle_seconds=0.3, check=healthy)
     ms, _, _ = time_steps(torch, dist, world, lambda: rs_step(rs_cand), steps, warm, flush)
     if world > 1:
         impl.set_option("stage_local", 1 if protocol == "pull" else 0)

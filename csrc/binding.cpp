@@ -154,6 +154,13 @@ std::vector<int64_t> all2all_plan(at::Tensor mLen_CPU, int64_t rank) {
   return out;
 }
 
+// The exception text check_status() produces for a block of status words (host only).
+std::string status_message(std::vector<int64_t> words, int64_t rank) {
+  FO_CHECK(static_cast<int>(words.size()) >= fo::kStatusWords, "a status block has ", fo::kStatusWords, " words");
+  if (words[fo::kStatusWordCode] == fo::kStatusOk) return "";
+  return fo::status_message(words.data(), static_cast<int>(rank));
+}
+
 }  // namespace
 
 TORCH_LIBRARY(flashoverlap_class, m) {
@@ -188,6 +195,7 @@ TORCH_LIBRARY(flashoverlap_class, m) {
       .def("gemm_reducescatter_fused", &OverlapImpl::GemmReduceScatterFused)
       .def("gemm_all2all_fused", &OverlapImpl::GemmAll2AllFused)
       .def("gemm_reducescatter_rmsnorm_fused", &OverlapImpl::GemmReduceScatterRmsNormFused)
+      .def("gemm_reducescatter_add_rmsnorm_fused", &OverlapImpl::GemmReduceScatterAddRmsNormFused)
       .def("set_option", &OverlapImpl::SetOption)
       .def("get_option", &OverlapImpl::GetOption)
       .def("symm_empty", &OverlapImpl::SymmEmpty)
@@ -213,4 +221,5 @@ TORCH_LIBRARY(flashoverlap_op, m) {
   m.def("algo_table", &algo_table);
   m.def("fused_loopback", &fo::fused_loopback);
   m.def("all2all_plan", &all2all_plan);
+  m.def("status_message", &status_message);
 }

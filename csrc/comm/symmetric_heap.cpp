@@ -88,6 +88,34 @@ SymmetricRegion* SymmetricHeap::allocate(size_t bytes, cudaStream_t stream) {
   return regions_.back().get();
 }
 
+void SymmetricHeap::release(SymmetricRegion* region, cudaStream_t stream) {
+  size_t idx = regions_.size();
+  for (size_t i = 0; i < regions_.size(); ++i) {
+    if (regions_[i].get() == region) idx = i;
+  }
+  if (idx == regions_.size()) return;  // not ours
+  if (region->owned) {
+    if (region->loopback || world_ == 1) {
+      for (void* p : region->ptr) {
+        if (p != nullptr) cudaFree(p);
+      }
+    } else {
+      for (int r = 0; r < world_; ++r) {
+        if (r != rank_ && region->ptr[r] != nullptr) cudaIpcCloseMemHandle(region->ptr[r]);
+      }
+      // nobody frees before everybody has unmapped
+      int* token = nullptr;
+      cuda_check(cudaMalloc(reinterpret_cast<void**>(&token), sizeof(int)), "cudaMalloc(token)");
+      cuda_check(cudaMemsetAsync(token, 0, sizeof(int), stream), "cudaMemsetAsync");
+      FO_NCCL_CHECK(ncclAllReduce(token, token, 1, ncclInt, ncclSum, comm_, stream));
+      cuda_check(cudaStreamSynchronize(stream), "cudaStreamSynchronize");
+      cudaFree(token);
+      cudaFree(region->ptr[rank_]);
+    }
+  }
+  regions_.erase(regions_.begin() + static_cast<long>(idx));
+}
+
 SymmetricRegion* SymmetricHeap::adopt(size_t bytes, const std::vector<void*>& ptrs, void* multicast) {
   auto region = std::make_unique<SymmetricRegion>();
   region->bytes = bytes;

@@ -45,11 +45,20 @@ class SymmetricHeap {
 
   // Collective.  The memory is zero-filled before any peer can see it.
   SymmetricRegion* allocate(size_t bytes, cudaStream_t stream);
+  // Collective: gives a region of allocate() back.  Every rank closes its mappings of the peers'
+  // copies, all ranks meet (so that nobody frees memory a peer still has mapped), then each
+  // frees its own copy.  The caller guarantees that no kernel on any rank still uses the region
+  // (true after a later allocate() on the same stream has returned: its handle exchange is
+  // ordered after everything enqueued before it on every rank).  Regions from adopt() are only
+  // forgotten.
+  void release(SymmetricRegion* region, cudaStream_t stream);
   // Records a symmetric buffer that somebody else allocated and mapped.
   SymmetricRegion* adopt(size_t bytes, const std::vector<void*>& ptrs, void* multicast);
   // Region of this heap that fully contains [p, p+n), or nullptr.
   const SymmetricRegion* find(const void* p, size_t n) const;
 
+  // The owner of the communicator is going away: no collective call may follow.
+  void detach_comm() { comm_ = nullptr; }
   int rank() const { return rank_; }
   int world() const { return world_; }
   bool loopback() const { return loopback_; }

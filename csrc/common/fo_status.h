@@ -7,6 +7,7 @@
 // The reference's wait kernel spins without a limit (src/wait.cuh:5-9).
 #pragma once
 #include <cstdint>
+#include <string>
 
 namespace fo {
 
@@ -44,6 +45,13 @@ inline const char* status_name(int32_t c) {
     case kStatusBadArgument: return "bad argument";
     default: return "unknown";
   }
+}
+
+// Text of a non-zero status block, as check_status() raises it.
+inline std::string status_message(const int64_t* words, int rank) {
+  return std::string("flashoverlap device status: ") + status_name(static_cast<int32_t>(words[kStatusWordCode])) +
+         " (args " + std::to_string(words[kStatusWordArg0]) + ", " + std::to_string(words[kStatusWordArg1]) + ", " +
+         std::to_string(words[kStatusWordArg2]) + ") on rank " + std::to_string(rank);
 }
 
 }  // namespace fo

@@ -98,8 +98,13 @@ struct GemmParams {
   // ReduceScatter with the RMSNorm tail fused into the reducers (row-major shard only): weight
   // [N] in the operands' type, per-row sums of squares [virtual rank][M / ws] (fp32, zero between
   // calls), per-row-panel counters of reduced tiles [virtual rank][tiles_m] (zero between calls).
+  // norm_res (optional): residual [M / ws, N] added to the reduced rows before they are stored
+  // and normalised (the stored rows are then the new residual stream; may alias the shard).
+  // norm_out (optional): where the normalised rows go; nullptr = over the shard itself.
   float norm_eps;
   const void* norm_w;
+  const void* norm_res[kMaxRanks];  // indexed by rank, like dst
+  void* norm_out[kMaxRanks];
   float* row_ssq;
   int* panel_cnt;
   // Timeline of the fused kernels (tracing builds of the kernel only): [virtual rank][tile]

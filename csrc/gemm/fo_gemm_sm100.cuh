@@ -163,136 +163,6 @@ __device__ __forceinline__ void unpack_add(uint32_t w, float& lo, float& hi) {
 }
 
 
-// Reduction of the row slices this rank owns of one tile: for every 16-byte vector the WS
-// partials are summed in fp32 and the rounded result is written to the output(s).  WS is a
-// template parameter so that the loads of several vectors (about 16 in flight per thread) can
-// be issued before the first sum: the loop is latency bound otherwise.
-template <int BN, bool BF16, int WS>
-__device__ __forceinline__ void reduce_tile(const GemmParams& p, int me, int rt, const uint8_t* src_tile,
-                                            size_t src_stride_bytes, size_t out_base, size_t out_ld) {
-  constexpr int kVecPerRow = BN / 8;
-  constexpr int kRowsOwned = kBM / WS;
-  constexpr int kTotalVec = kRowsOwned * kVecPerRow;
-  constexpr int U = (16 / WS) < 1 ? 1 : (16 / WS);  // vectors per thread per round
-  static_assert(kTotalVec % (kReducerThreads * U) == 0, "tile slice must split evenly over the reducer threads");
-  const bool ar = p.comm == kCommFusedAR;
-  for (int v0 = rt; v0 < kTotalVec; v0 += kReducerThreads * U) {
-    uint4 x[U][WS];
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const int v = v0 + u * kReducerThreads;
-      const int q = v / kVecPerRow;
-      const int c8 = v - q * kVecPerRow;
-      const uint8_t* sp = src_tile + (static_cast<size_t>(q) * BN + c8 * 8) * 2;
-#pragma unroll
-      for (int s = 0; s < WS; ++s) x[u][s] = ptx::ld_cg_v4(sp + static_cast<size_t>(s) * src_stride_bytes);
-    }
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const int v = v0 + u * kReducerThreads;
-      const int q = v / kVecPerRow;
-      const int c8 = v - q * kVecPerRow;
-      float a[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) a[i] = 0.f;
-#pragma unroll
-      for (int s = 0; s < WS; ++s) {
-        unpack_add<BF16>(x[u][s].x, a[0], a[1]);
-        unpack_add<BF16>(x[u][s].y, a[2], a[3]);
-        unpack_add<BF16>(x[u][s].z, a[4], a[5]);
-        unpack_add<BF16>(x[u][s].w, a[6], a[7]);
-      }
-      uint4 y;
-      y.x = pack2<BF16>(a[0], a[1]);
-      y.y = pack2<BF16>(a[2], a[3]);
-      y.z = pack2<BF16>(a[4], a[5]);
-      y.w = pack2<BF16>(a[6], a[7]);
-      if (ar) {
-        const int lr = p.strided_rows ? (q * WS + me) : (me * kRowsOwned + q);
-        const size_t off = (out_base + static_cast<size_t>(lr) * out_ld + c8 * 8) * 2;
-        if (p.mc_dst != nullptr) {
-          // NVLS: one store, replicated by the switch into every rank's output
-          ptx::multimem_st_v4(reinterpret_cast<uint8_t*>(p.mc_dst) + off, y);
-        } else {
-#pragma unroll
-          for (int d = 0; d < WS; ++d) {
-            const int dd = (me + d) % WS;  // start with the local copy, then fan out
-            ptx::st_v4(reinterpret_cast<uint8_t*>(p.dst[dd]) + off, y);
-          }
-        }
-      } else {
-        const size_t off = (out_base + static_cast<size_t>(q) * out_ld + c8 * 8) * 2;
-        ptx::st_v4(reinterpret_cast<uint8_t*>(p.dst[me]) + off, y);
-      }
-    }
-  }
-}
-
-// ReduceScatter reduction that also gathers the RMSNorm statistics: sums the WS partials of the
-// owned rows of one tile, writes the rounded sums to the row-major local shard and adds each
-// row's sum of squares (of the rounded values, as a separate norm kernel would see them) to
-// row_ssq.  One row of a tile is BN / 8 vectors = a whole warp (BN = 256) or half of one.
-template <int BN, bool BF16, int WS>
-__device__ __forceinline__ void reduce_tile_ssq(const GemmParams& p, int me, int rt, const uint8_t* src_tile,
-                                                size_t src_stride_bytes, size_t out_base, float* row_ssq) {
-  constexpr int kVecPerRow = BN / 8;
-  constexpr int kRowsOwned = kBM / WS;
-  constexpr int kTotalVec = kRowsOwned * kVecPerRow;
-  constexpr int U = (16 / WS) < 1 ? 1 : (16 / WS);
-  static_assert(kTotalVec % (kReducerThreads * U) == 0, "tile slice must split evenly over the reducer threads");
-  static_assert(kVecPerRow == 32 || kVecPerRow == 16, "a row must be a warp or half a warp of vectors");
-  const int lane = rt & 31;
-  for (int v0 = rt; v0 < kTotalVec; v0 += kReducerThreads * U) {
-    uint4 x[U][WS];
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const int v = v0 + u * kReducerThreads;
-      const int q = v / kVecPerRow;
-      const int c8 = v - q * kVecPerRow;
-      const uint8_t* sp = src_tile + (static_cast<size_t>(q) * BN + c8 * 8) * 2;
-#pragma unroll
-      for (int s = 0; s < WS; ++s) x[u][s] = ptx::ld_cg_v4(sp + static_cast<size_t>(s) * src_stride_bytes);
-    }
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const int v = v0 + u * kReducerThreads;
-      const int q = v / kVecPerRow;
-      const int c8 = v - q * kVecPerRow;
-      float a[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) a[i] = 0.f;
-#pragma unroll
-      for (int s = 0; s < WS; ++s) {
-        unpack_add<BF16>(x[u][s].x, a[0], a[1]);
-        unpack_add<BF16>(x[u][s].y, a[2], a[3]);
-        unpack_add<BF16>(x[u][s].z, a[4], a[5]);
-        unpack_add<BF16>(x[u][s].w, a[6], a[7]);
-      }
-      uint4 y;
-      y.x = pack2<BF16>(a[0], a[1]);
-      y.y = pack2<BF16>(a[2], a[3]);
-      y.z = pack2<BF16>(a[4], a[5]);
-      y.w = pack2<BF16>(a[6], a[7]);
-      const size_t off = (out_base + static_cast<size_t>(q) * p.N + c8 * 8) * 2;
-      ptx::st_v4(reinterpret_cast<uint8_t*>(p.dst[me]) + off, y);
-      // sum of squares of the rounded values
-      float r[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) r[i] = 0.f;
-      unpack_add<BF16>(y.x, r[0], r[1]);
-      unpack_add<BF16>(y.y, r[2], r[3]);
-      unpack_add<BF16>(y.z, r[4], r[5]);
-      unpack_add<BF16>(y.w, r[6], r[7]);
-      float ss = 0.f;
-#pragma unroll
-      for (int i = 0; i < 8; ++i) ss += r[i] * r[i];
-#pragma unroll
-      for (int o = kVecPerRow / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-      if ((lane & (kVecPerRow - 1)) == 0) atomicAdd(row_ssq + q, ss);
-    }
-  }
-}
-
 // y = round16(round16(x * scale) * w), the arithmetic of the stand-alone RMSNorm kernels.
 template <bool BF16>
 __device__ __forceinline__ uint32_t norm_scale_mul2(uint32_t x, uint32_t w, float scale) {
@@ -309,16 +179,171 @@ __device__ __forceinline__ uint32_t norm_scale_mul2(uint32_t x, uint32_t w, floa
   }
 }
 
+// round16(a + b) per 16-bit pair, added in fp32: what `a + b` on 16-bit tensors computes.
+template <bool BF16>
+__device__ __forceinline__ uint32_t add2(uint32_t a, uint32_t b) {
+  float lo = 0.f, hi = 0.f;
+  unpack_add<BF16>(a, lo, hi);
+  unpack_add<BF16>(b, lo, hi);
+  return pack2<BF16>(lo, hi);
+}
+
+// Where the reduced vectors of one tile go.  AllReduce: every rank's output (one multimem.st
+// when the output has an NVSwitch multicast mapping, else one peer store per rank).
+// ReduceScatter: the local shard.  With NORM (reduce-scatter into the row-major shard) the sink
+// also adds the optional residual and gathers each row's sum of squares of the stored values,
+// as a separate norm kernel would see them.  Vector v of a tile slice is its bytes
+// [16 v, 16 v + 16): rows of the slice are BN * 2 bytes long.
+template <int BN, bool BF16, int WS, bool NORM>
+struct TileSink {
+  static constexpr int kVecPerRow = BN / 8;
+  static constexpr int kRowsOwned = kBM / WS;
+  const GemmParams& p;
+  int me;
+  size_t out_base;  // element offset of (tile row 0, col 0) in the destination
+  size_t out_ld;
+  float* row_ssq;   // NORM: sums of squares of the rows this tile's slice belongs to
+  int lane;
+
+  __device__ __forceinline__ void put(int v, uint4 y) const {
+    const int q = v / kVecPerRow;
+    const int c8 = v - q * kVecPerRow;
+    if (p.comm == kCommFusedAR) {
+      const int lr = p.strided_rows ? (q * WS + me) : (me * kRowsOwned + q);
+      const size_t off = (out_base + static_cast<size_t>(lr) * out_ld + c8 * 8) * 2;
+      if (p.mc_dst != nullptr) {
+        // NVLS: one store, replicated by the switch into every rank's output
+        ptx::multimem_st_v4(reinterpret_cast<uint8_t*>(p.mc_dst) + off, y);
+      } else {
+#pragma unroll
+        for (int d = 0; d < WS; ++d) {
+          const int dd = (me + d) % WS;  // start with the local copy, then fan out
+          ptx::st_v4(reinterpret_cast<uint8_t*>(p.dst[dd]) + off, y);
+        }
+      }
+      return;
+    }
+    const size_t off = (out_base + static_cast<size_t>(q) * out_ld + c8 * 8) * 2;
+    if constexpr (NORM) {
+      if (p.norm_res[me] != nullptr) {
+        const uint4 r = ptx::ld_cg_v4(reinterpret_cast<const uint8_t*>(p.norm_res[me]) + off);
+        y.x = add2<BF16>(y.x, r.x);
+        y.y = add2<BF16>(y.y, r.y);
+        y.z = add2<BF16>(y.z, r.z);
+        y.w = add2<BF16>(y.w, r.w);
+      }
+    }
+    ptx::st_v4(reinterpret_cast<uint8_t*>(p.dst[me]) + off, y);
+    if constexpr (NORM) {
+      static_assert(kVecPerRow == 32 || kVecPerRow == 16, "a row must be a warp or half a warp of vectors");
+      float r[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) r[i] = 0.f;
+      unpack_add<BF16>(y.x, r[0], r[1]);
+      unpack_add<BF16>(y.y, r[2], r[3]);
+      unpack_add<BF16>(y.z, r[4], r[5]);
+      unpack_add<BF16>(y.w, r[6], r[7]);
+      float ss = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) ss += r[i] * r[i];
+#pragma unroll
+      for (int o = kVecPerRow / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      if ((lane & (kVecPerRow - 1)) == 0) atomicAdd(row_ssq + q, ss);
+    }
+  }
+};
+
+template <bool BF16, int WS>
+__device__ __forceinline__ uint4 sum_partials(const uint4 (&x)[WS]) {
+  float a[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) a[i] = 0.f;
+#pragma unroll
+  for (int s = 0; s < WS; ++s) {
+    unpack_add<BF16>(x[s].x, a[0], a[1]);
+    unpack_add<BF16>(x[s].y, a[2], a[3]);
+    unpack_add<BF16>(x[s].z, a[4], a[5]);
+    unpack_add<BF16>(x[s].w, a[6], a[7]);
+  }
+  uint4 y;
+  y.x = pack2<BF16>(a[0], a[1]);
+  y.y = pack2<BF16>(a[2], a[3]);
+  y.z = pack2<BF16>(a[4], a[5]);
+  y.w = pack2<BF16>(a[6], a[7]);
+  return y;
+}
+
+// Reduction of the row slices this rank owns of one tile: for every 16-byte vector the WS
+// partials are summed in fp32 and the rounded result is handed to the sink.  WS is a template
+// parameter so that the loads of several vectors (about 16 in flight per thread) can be issued
+// before the first sum: the loop is latency bound otherwise.
+//
+// Where the partials are: push protocol - WS slices in THIS rank's staging, `stride` bytes
+// apart, starting at src0; pull protocol - the same offset `tile_off` of EVERY rank's staging:
+// with a multicast mapping of the staging one multimem.ld_reduce per vector lets the NVSwitch
+// fetch and sum all ranks' copies (fp32 accumulation), so only the result crosses this GPU's
+// links; otherwise each vector is loaded from every rank over NVLink and summed here.
+template <int BN, bool BF16, int WS, bool NORM>
+__device__ __forceinline__ void reduce_tile(const GemmParams& p, int me, int rt, const uint8_t* src0, size_t stride,
+                                            size_t tile_off, const TileSink<BN, BF16, WS, NORM>& sink) {
+  constexpr int kVecPerRow = BN / 8;
+  constexpr int kRowsOwned = kBM / WS;
+  constexpr int kTotalVec = kRowsOwned * kVecPerRow;
+  constexpr int kPerThread = kTotalVec / kReducerThreads;
+  constexpr int U = (16 / WS) < 1 ? 1 : (16 / WS);  // vectors per thread per round (WS loads each)
+  // vectors per thread per round of the switch-side reduction (measured at 2 GPUs: 8 in flight
+  // per thread were slower than 4 on a communication-bound shape)
+  constexpr int UM = kPerThread >= 4 ? 4 : kPerThread;
+  static_assert(kTotalVec % (kReducerThreads * U) == 0 && kTotalVec % (kReducerThreads * UM) == 0,
+                "tile slice must split evenly over the reducer threads");
+
+  if (p.stage_local && p.mc_stage != nullptr) {
+    const uint8_t* mc = reinterpret_cast<const uint8_t*>(p.mc_stage) + tile_off;
+    for (int v0 = rt; v0 < kTotalVec; v0 += kReducerThreads * UM) {
+      uint4 y[UM];
+#pragma unroll
+      for (int u = 0; u < UM; ++u) {
+        y[u] = ptx::multimem_ld_reduce_add_v4<BF16>(mc + static_cast<size_t>(v0 + u * kReducerThreads) * 16);
+      }
+#pragma unroll
+      for (int u = 0; u < UM; ++u) sink.put(v0 + u * kReducerThreads, y[u]);
+    }
+    return;
+  }
+
+  const uint8_t* src[WS];
+#pragma unroll
+  for (int s = 0; s < WS; ++s) {
+    src[s] = p.stage_local ? reinterpret_cast<const uint8_t*>(p.stage[(me + s) % WS]) + tile_off
+                           : src0 + static_cast<size_t>(s) * stride;
+  }
+  for (int v0 = rt; v0 < kTotalVec; v0 += kReducerThreads * U) {
+    uint4 x[U][WS];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const size_t voff = static_cast<size_t>(v0 + u * kReducerThreads) * 16;
+#pragma unroll
+      for (int s = 0; s < WS; ++s) x[u][s] = ptx::ld_cg_v4(src[s] + voff);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) sink.put(v0 + u * kReducerThreads, sum_partials<BF16, WS>(x[u]));
+  }
+}
+
 // RMSNorm of the `rows` shard rows starting at `row0` (all their tiles have been reduced and
-// their sums of squares are complete): normalises in place.  A thread keeps kJV weight vectors
-// in registers and walks down the rows two at a time, so 2 * kJV loads are in flight per
-// thread; the rows were written moments ago and come from L2.
+// their sums of squares are complete): reads the rows from the shard and writes the normalised
+// rows to `out` (the shard itself, or a second buffer when the un-normalised rows are kept as
+// the residual stream).  A thread keeps kJV weight vectors in registers and walks down the rows
+// two at a time, so 2 * kJV loads are in flight per thread; the rows were written moments ago
+// and come from L2.
 template <bool BF16>
 __device__ __forceinline__ void normalise_panel(const GemmParams& p, int me, int rt, int row0, int rows,
                                                 const float* row_ssq) {
   constexpr int kJV = 4;
   const int nvec = p.N / 8;
-  uint8_t* base = reinterpret_cast<uint8_t*>(p.dst[me]) + static_cast<size_t>(row0) * p.N * 2;
+  const uint8_t* base = reinterpret_cast<const uint8_t*>(p.dst[me]) + static_cast<size_t>(row0) * p.N * 2;
+  uint8_t* obase = reinterpret_cast<uint8_t*>(p.norm_out[me] != nullptr ? p.norm_out[me] : p.dst[me]) +
+                   static_cast<size_t>(row0) * p.N * 2;
   const uint8_t* w = reinterpret_cast<const uint8_t*>(p.norm_w);
   const size_t pitch = static_cast<size_t>(p.N) * 2;
   const float inv_n = 1.f / static_cast<float>(p.N);
@@ -351,7 +376,7 @@ __device__ __forceinline__ void normalise_panel(const GemmParams& p, int me, int
             y.y = norm_scale_mul2<BF16>(x[r][i].y, wv[i].y, scale);
             y.z = norm_scale_mul2<BF16>(x[r][i].z, wv[i].z, scale);
             y.w = norm_scale_mul2<BF16>(x[r][i].w, wv[i].w, scale);
-            ptx::st_v4(base + (q + r) * pitch + static_cast<size_t>(j) * 16, y);
+            ptx::st_v4(obase + (q + r) * pitch + static_cast<size_t>(j) * 16, y);
           }
         }
       }
@@ -359,93 +384,39 @@ __device__ __forceinline__ void normalise_panel(const GemmParams& p, int me, int
   }
 }
 
-// Pull variant of the reduction: the partials of the rows this rank owns sit at the same offset
-// `tile_off` (bytes) of EVERY rank's staging buffer.  With a multicast mapping of the staging one
-// multimem.ld_reduce per vector lets the NVSwitch fetch and sum all ranks' copies (fp32
-// accumulation), so only the result crosses this GPU's links; otherwise each vector is loaded
-// from every rank over NVLink and summed here.
-template <int BN, bool BF16, int WS>
-__device__ __forceinline__ void reduce_tile_pull(const GemmParams& p, int me, int rt, size_t tile_off,
-                                                 size_t out_base, size_t out_ld) {
-  constexpr int kVecPerRow = BN / 8;
+// One tile's reduction for a world size known at compile time, followed (NORM) by the
+// normalisation of the tile's row panel when this was the panel's last tile.
+template <int BN, bool BF16, int WS, bool NORM>
+__device__ __forceinline__ void reduce_one_tile(const GemmParams& p, int me, int vr, int rt, int t, int tile_m,
+                                                size_t out_base, size_t out_ld, const uint8_t* src0, size_t stride,
+                                                size_t tile_off, volatile int* s_is_last) {
   constexpr int kRowsOwned = kBM / WS;
-  constexpr int kTotalVec = kRowsOwned * kVecPerRow;
-  const bool ar = p.comm == kCommFusedAR;
-  const bool sw_reduce = p.mc_stage != nullptr;
-  constexpr int U = (16 / WS) < 1 ? 1 : (16 / WS);  // vectors per thread per round (peer loads)
-  // vectors per thread per round (switch reduction)
-  // (8 x 16 B per thread = 16 KB per CTA in flight: a switch-side reduction takes several
-  // microseconds to answer, and only requests in flight keep the links busy)
-  constexpr int UM = (kTotalVec / kReducerThreads) >= 8 ? 8 : ((kTotalVec / kReducerThreads) >= 4 ? 4 : (kTotalVec / kReducerThreads));
-  static_assert(kTotalVec % (kReducerThreads * U) == 0 && kTotalVec % (kReducerThreads * UM) == 0,
-                "tile slice must split evenly over the reducer threads");
-
-  auto store_result = [&](int v, const uint4& y) {
-    const int q = v / kVecPerRow;
-    const int c8 = v - q * kVecPerRow;
-    if (ar) {
-      const int lr = p.strided_rows ? (q * WS + me) : (me * kRowsOwned + q);
-      const size_t off = (out_base + static_cast<size_t>(lr) * out_ld + c8 * 8) * 2;
-      if (p.mc_dst != nullptr) {
-        ptx::multimem_st_v4(reinterpret_cast<uint8_t*>(p.mc_dst) + off, y);
-      } else {
-#pragma unroll
-        for (int d = 0; d < WS; ++d) {
-          const int dd = (me + d) % WS;
-          ptx::st_v4(reinterpret_cast<uint8_t*>(p.dst[dd]) + off, y);
-        }
-      }
-    } else {
-      const size_t off = (out_base + static_cast<size_t>(q) * out_ld + c8 * 8) * 2;
-      ptx::st_v4(reinterpret_cast<uint8_t*>(p.dst[me]) + off, y);
+  TileSink<BN, BF16, WS, NORM> sink{p, me, out_base, out_ld, nullptr, rt & 31};
+  if constexpr (NORM) {
+    // Reduce into the row-major shard while gathering each row's sum of squares; whoever
+    // reduces the last tile of a row panel normalises the panel, whose rows were written
+    // moments ago and are still in L2.
+    float* ssq = p.row_ssq + static_cast<size_t>(vr) * (p.M / WS) + static_cast<size_t>(tile_m) * kRowsOwned;
+    int* cnt = p.panel_cnt + vr * p.tiles_m + tile_m;
+    sink.row_ssq = ssq;
+    reduce_tile<BN, BF16, WS, NORM>(p, me, rt, src0, stride, tile_off, sink);
+    ptx::named_bar_sync(2, kReducerThreads);  // every thread's stores and atomics are issued
+    if (rt == 0) {
+      __threadfence();
+      const int old = atomicAdd(cnt, 1);
+      *s_is_last = (old == p.tiles_n - 1) ? 1 : 0;
+      if (old == p.tiles_n - 1) __threadfence();
     }
-  };
-
-  if (sw_reduce) {
-    const uint8_t* mc = reinterpret_cast<const uint8_t*>(p.mc_stage) + tile_off;
-    for (int v0 = rt; v0 < kTotalVec; v0 += kReducerThreads * UM) {
-      uint4 y[UM];
-#pragma unroll
-      for (int u = 0; u < UM; ++u) {
-        // vector v of the slice is its bytes [16 v, 16 v + 16): rows are BN * 2 bytes apart
-        y[u] = ptx::multimem_ld_reduce_add_v4<BF16>(mc + static_cast<size_t>(v0 + u * kReducerThreads) * 16);
-      }
-#pragma unroll
-      for (int u = 0; u < UM; ++u) store_result(v0 + u * kReducerThreads, y[u]);
+    ptx::named_bar_sync(2, kReducerThreads);
+    if (*s_is_last) {
+      normalise_panel<BF16>(p, me, rt, tile_m * kRowsOwned, kRowsOwned, ssq);
+      ptx::named_bar_sync(2, kReducerThreads);
+      if (rt < kRowsOwned) ssq[rt] = 0.f;
+      if (rt == 0) *cnt = 0;
     }
-    return;
-  }
-
-  const uint8_t* src[WS];
-#pragma unroll
-  for (int s = 0; s < WS; ++s) src[s] = reinterpret_cast<const uint8_t*>(p.stage[(me + s) % WS]) + tile_off;
-  for (int v0 = rt; v0 < kTotalVec; v0 += kReducerThreads * U) {
-    uint4 x[U][WS];
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const size_t voff = static_cast<size_t>(v0 + u * kReducerThreads) * 16;
-#pragma unroll
-      for (int s = 0; s < WS; ++s) x[u][s] = ptx::ld_cg_v4(src[s] + voff);
-    }
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      float a[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) a[i] = 0.f;
-#pragma unroll
-      for (int s = 0; s < WS; ++s) {
-        unpack_add<BF16>(x[u][s].x, a[0], a[1]);
-        unpack_add<BF16>(x[u][s].y, a[2], a[3]);
-        unpack_add<BF16>(x[u][s].z, a[4], a[5]);
-        unpack_add<BF16>(x[u][s].w, a[6], a[7]);
-      }
-      uint4 y;
-      y.x = pack2<BF16>(a[0], a[1]);
-      y.y = pack2<BF16>(a[2], a[3]);
-      y.z = pack2<BF16>(a[4], a[5]);
-      y.w = pack2<BF16>(a[6], a[7]);
-      store_result(v0 + u * kReducerThreads, y);
-    }
+    ptx::named_bar_sync(2, kReducerThreads);  // s_is_last is reused by the next tile
+  } else {
+    reduce_tile<BN, BF16, WS, NORM>(p, me, rt, src0, stride, tile_off, sink);
   }
 }
 
@@ -1058,49 +1029,18 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
 
         const size_t stride_b = src_stride * 2;
         if (p.diag & 1) continue;
-        if constexpr (NORM) {
-          // ReduceScatter + RMSNorm: reduce into the row-major shard while gathering each row's
-          // sum of squares; whoever reduces the last tile of a row panel normalises the panel,
-          // whose rows were written moments ago and are still in L2.
-          float* ssq = p.row_ssq + static_cast<size_t>(vr) * (p.M / ws) + static_cast<size_t>(tc.m) * rows_owned;
-          int* cnt = p.panel_cnt + vr * p.tiles_m + tc.m;
-          switch (ws) {
-            case 2: reduce_tile_ssq<BN, BF16, 2>(p, me, rt, src_tile, stride_b, out_base, ssq); break;
-            case 4: reduce_tile_ssq<BN, BF16, 4>(p, me, rt, src_tile, stride_b, out_base, ssq); break;
-            default: reduce_tile_ssq<BN, BF16, 8>(p, me, rt, src_tile, stride_b, out_base, ssq); break;
-          }
-          ptx::named_bar_sync(2, kReducerThreads);  // every thread's stores and atomics are issued
-          if (rt == 0) {
-            __threadfence();
-            const int old = atomicAdd(cnt, 1);
-            *s_is_last = (old == p.tiles_n - 1) ? 1 : 0;
-            if (old == p.tiles_n - 1) __threadfence();
-          }
-          ptx::named_bar_sync(2, kReducerThreads);
-          if (*s_is_last) {
-            normalise_panel<BF16>(p, me, rt, tc.m * rows_owned, rows_owned, ssq);
-            ptx::named_bar_sync(2, kReducerThreads);
-            if (rt < rows_owned) ssq[rt] = 0.f;
-            if (rt == 0) *cnt = 0;
-          }
-          ptx::named_bar_sync(2, kReducerThreads);  // s_is_last is reused by the next tile
-          continue;
-        }
-        if (p.stage_local) {
-          // rows of owner `me` inside tile t's [owner][rows owned][BN] block of any rank's staging
-          const size_t tile_off = (static_cast<size_t>(t) * kBM + static_cast<size_t>(me) * rows_owned) * BN * 2;
-          switch (ws) {
-            case 2: reduce_tile_pull<BN, BF16, 2>(p, me, rt, tile_off, out_base, out_ld); break;
-            case 4: reduce_tile_pull<BN, BF16, 4>(p, me, rt, tile_off, out_base, out_ld); break;
-            default: reduce_tile_pull<BN, BF16, 8>(p, me, rt, tile_off, out_base, out_ld); break;
-          }
-          if (rt == 0) stamp(t, kTraceReduced);
-          continue;
-        }
+        // pull protocol: rows of owner `me` inside tile t's [owner][rows owned][BN] block of any rank's staging
+        const size_t tile_off = (static_cast<size_t>(t) * kBM + static_cast<size_t>(me) * rows_owned) * BN * 2;
         switch (ws) {
-          case 2: reduce_tile<BN, BF16, 2>(p, me, rt, src_tile, stride_b, out_base, out_ld); break;
-          case 4: reduce_tile<BN, BF16, 4>(p, me, rt, src_tile, stride_b, out_base, out_ld); break;
-          default: reduce_tile<BN, BF16, 8>(p, me, rt, src_tile, stride_b, out_base, out_ld); break;
+          case 2:
+            reduce_one_tile<BN, BF16, 2, NORM>(p, me, vr, rt, t, tc.m, out_base, out_ld, src_tile, stride_b, tile_off, s_is_last);
+            break;
+          case 4:
+            reduce_one_tile<BN, BF16, 4, NORM>(p, me, vr, rt, t, tc.m, out_base, out_ld, src_tile, stride_b, tile_off, s_is_last);
+            break;
+          default:
+            reduce_one_tile<BN, BF16, 8, NORM>(p, me, vr, rt, t, tc.m, out_base, out_ld, src_tile, stride_b, tile_off, s_is_last);
+            break;
         }
         if (rt == 0) stamp(t, kTraceReduced);
       }

@@ -17,7 +17,9 @@ std::vector<int64_t> fused_loopback(std::string comm_op, std::vector<at::Tensor>
                                     int64_t timeout_ms, bool stage_local,
                                     c10::optional<at::Tensor> mlen_opt,
                                     c10::optional<at::Tensor> norm_w, double norm_eps,
-                                    c10::optional<at::Tensor> trace, int64_t epi_bufs, int64_t pull_direct) {
+                                    c10::optional<at::Tensor> trace, int64_t epi_bufs, int64_t pull_direct,
+                                    c10::optional<std::vector<at::Tensor>> norm_res,
+                                    c10::optional<std::vector<at::Tensor>> norm_out) {
   const at::Tensor RA = RA_opt.has_value() ? *RA_opt : at::Tensor();
   const at::Tensor cseg_gpu = cseg_opt.has_value() ? *cseg_opt : at::Tensor();
   const int ws = static_cast<int>(A.size());
@@ -113,8 +115,7 @@ std::vector<int64_t> fused_loopback(std::string comm_op, std::vector<at::Tensor>
   }
   at::Tensor row_ssq, panel_cnt;  // RMSNorm tail: statistics of every virtual rank
   if (norm_w.has_value()) {
-    FO_CHECK(comm == kCommFusedRS && natural_out && !stage_local,
-             "the RMSNorm tail needs a row-major reduce-scatter with the push protocol");
+    FO_CHECK(comm == kCommFusedRS && natural_out, "the RMSNorm tail needs a row-major reduce-scatter");
     FO_CHECK(norm_w->is_cuda() && norm_w->is_contiguous() && norm_w->scalar_type() == A[0].scalar_type() &&
                  norm_w->numel() == p.N,
              "norm_w must be a contiguous CUDA tensor of N elements in the operands' dtype");
@@ -125,6 +126,23 @@ std::vector<int64_t> fused_loopback(std::string comm_op, std::vector<at::Tensor>
     p.norm_eps = static_cast<float>(norm_eps);
     p.row_ssq = row_ssq.data_ptr<float>();
     p.panel_cnt = panel_cnt.data_ptr<int>();
+    const int64_t shard = static_cast<int64_t>(p.M / ws) * p.N;
+    if (norm_res.has_value()) {
+      FO_CHECK(static_cast<int>(norm_res->size()) == ws, "norm_res needs one tensor per rank");
+      for (int r = 0; r < ws; ++r) {
+        check_out((*norm_res)[r], A[0], shard, "norm_res");
+        p.norm_res[r] = (*norm_res)[r].data_ptr();
+      }
+    }
+    if (norm_out.has_value()) {
+      FO_CHECK(static_cast<int>(norm_out->size()) == ws, "norm_out needs one tensor per rank");
+      for (int r = 0; r < ws; ++r) {
+        check_out((*norm_out)[r], A[0], shard, "norm_out");
+        p.norm_out[r] = (*norm_out)[r].data_ptr();
+      }
+    }
+  } else {
+    FO_CHECK(!norm_res.has_value() && !norm_out.has_value(), "norm_res / norm_out belong to the RMSNorm tail (norm_w)");
   }
   if (const char* d = std::getenv("FLASHOVERLAP_DIAG")) p.diag = std::atoi(d);  // timing studies only
   p.timeout_ns = static_cast<uint64_t>(timeout_ms) * 1000000ull;

@@ -24,7 +24,9 @@ namespace fo {
 // the call-to-call handshake.  stage_local selects the pull protocol (partials staged in the
 // producing rank's own memory, owners fetch them; here without a multicast mapping, so with one
 // load per rank); pull_direct != 0 with it: the epilogue threads store the partial tiles themselves
-// instead of handing them to the push warp's TMA stores.  Returns ws * kStatusWords status words.
+// instead of handing them to the push warp's TMA stores.  norm_res / norm_out (with norm_w): per-rank
+// residual added to the reduced rows before they are stored in out[r] and normalised, and per-rank
+// destination of the normalised rows (default: over out[r]).  Returns ws * kStatusWords status words.
 std::vector<int64_t> fused_loopback(std::string comm_op, std::vector<at::Tensor> A,
                                     std::vector<at::Tensor> B, std::vector<at::Tensor> out,
                                     c10::optional<at::Tensor> RA,
@@ -33,6 +35,8 @@ std::vector<int64_t> fused_loopback(std::string comm_op, std::vector<at::Tensor>
                                     int64_t timeout_ms, bool stage_local,
                                     c10::optional<at::Tensor> mlen,
                                     c10::optional<at::Tensor> norm_w, double norm_eps,
-                                    c10::optional<at::Tensor> trace, int64_t epi_bufs, int64_t pull_direct);
+                                    c10::optional<at::Tensor> trace, int64_t epi_bufs, int64_t pull_direct,
+                                    c10::optional<std::vector<at::Tensor>> norm_res,
+                                    c10::optional<std::vector<at::Tensor>> norm_out);
 
 }  // namespace fo

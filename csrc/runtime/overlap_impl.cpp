@@ -22,6 +22,9 @@ OverlapImpl::~OverlapImpl() {
   if (comm_done_ != nullptr) cudaEventDestroy(comm_done_);
   if (gemm_start_ != nullptr) cudaEventDestroy(gemm_start_);
   if (comm_stream_ != nullptr) cudaStreamDestroy(comm_stream_);
+  // Tensors from symm_empty may keep the heap (and its memory) alive beyond this point; the heap
+  // needs the communicator only for collective calls, which nobody can make any more.
+  if (heap_ != nullptr) heap_->detach_comm();
   heap_.reset();
   if (comm_ != nullptr) ncclCommDestroy(comm_);  // the reference never destroys its communicator
 }
@@ -55,7 +58,7 @@ void OverlapImpl::NcclInit(int64_t rank, int64_t world, std::vector<int64_t> id)
     ncclUniqueId uid = unpack_nccl_id(id);
     FO_NCCL_CHECK(ncclCommInitRank(&comm_, world_, uid, rank_));
   }
-  heap_ = std::make_unique<SymmetricHeap>(rank_, world_, comm_, false);
+  heap_ = std::make_shared<SymmetricHeap>(rank_, world_, comm_, false);
   status_ = at::zeros({kStatusWords}, at::TensorOptions().dtype(at::kInt).device(at::kCUDA, device_));
 }
 
@@ -160,8 +163,10 @@ at::Tensor OverlapImpl::SymmEmpty(std::vector<int64_t> sizes, std::string dtype)
   }
   const size_t bytes = std::max<size_t>(static_cast<size_t>(numel) * c10::elementSize(st), 256);
   SymmetricRegion* reg = heap_->allocate(bytes, stream());
-  // The region belongs to this object; the tensor is a view and must not outlive it.
-  return at::from_blob(reg->local(), sizes, [](void*) {},
+  // The memory belongs to the heap, and the tensor shares ownership of the heap: it stays valid
+  // even if it outlives this object (the heap then goes with the last such tensor).
+  std::shared_ptr<SymmetricHeap> keep = heap_;
+  return at::from_blob(reg->local(), sizes, [keep](void*) {},
                        at::TensorOptions().dtype(st).device(at::kCUDA, device_));
 }
 
@@ -205,9 +210,7 @@ std::vector<int64_t> OverlapImpl::ReadStatus() {
 
 void OverlapImpl::CheckStatus() {
   const std::vector<int64_t> s = ReadStatus();
-  FO_CHECK(s[kStatusWordCode] == kStatusOk, "flashoverlap device status: ",
-              status_name(static_cast<int32_t>(s[kStatusWordCode])), " (args ", s[kStatusWordArg0],
-              ", ", s[kStatusWordArg1], ", ", s[kStatusWordArg2], ") on rank ", rank_);
+  FO_CHECK(s[kStatusWordCode] == kStatusOk, status_message(s.data(), rank_));
 }
 
 void OverlapImpl::ResetStatus() {
@@ -419,16 +422,20 @@ void OverlapImpl::ensure_fused_buffers(size_t stage_bytes, size_t nflags, bool p
   if (signal_ == nullptr) signal_ = heap_->allocate(kSignalBytes, stream());
   const bool user_stage = pull && user_stage_ != nullptr && user_stage_->bytes >= stage_bytes;
   if (!user_stage && (stage_ == nullptr || stage_->bytes < stage_bytes)) {
-    // A larger shape than any seen so far: take a new region (the old one stays mapped until
-    // this object dies, peers may still hold its address).
+    // A larger shape than any seen so far: take a new region, then give the old one back.  The
+    // new region's handle exchange is a stream-ordered collective followed by a synchronise, so
+    // every rank's earlier fused calls - the last users of the old region - have finished.
+    SymmetricRegion* old = stage_;
     stage_ = heap_->allocate(stage_bytes, stream());
+    if (old != nullptr) heap_->release(old, stream());
   }
 }
 
 void OverlapImpl::run_fused(int comm, const at::Tensor& A, const at::Tensor& B, at::Tensor out,
                             int out_mode, const int* RA, int rldn, int* MM, int mm_stride,
                             bool monitor, const int* cseg, int num_groups, int algo,
-                            const at::Tensor* norm_w, double norm_eps) {
+                            const at::Tensor* norm_w, double norm_eps, const at::Tensor* norm_res,
+                            const at::Tensor* norm_out) {
   FO_CHECK(heap_ != nullptr, "call nccl_init first");
   c10::cuda::CUDAGuard guard(A.device());
   FO_CHECK(kBM % world_ == 0, "world size must divide the tile height 128");
@@ -442,9 +449,8 @@ void OverlapImpl::run_fused(int comm, const at::Tensor& A, const at::Tensor& B, 
   const size_t full_bytes = static_cast<size_t>(p.M) * p.N * 2;
   const size_t nflags = (num_groups > 0 && cseg != nullptr) ? num_groups : p.num_tiles;
   // Pull protocol: partials stay in the producing rank's staging; a staging buffer with a
-  // multicast mapping (use_stage) lets the switch do the summation.  (The RMSNorm tail is
-  // written for the push protocol.)
-  const bool pull = opt_stage_local_ != 0 && norm_w == nullptr;
+  // multicast mapping (use_stage) lets the switch do the summation.
+  const bool pull = opt_stage_local_ != 0;
   ensure_fused_buffers(full_bytes, nflags, pull);
 
   const size_t out_bytes = comm == kCommFusedAR ? full_bytes : full_bytes / world_;
@@ -459,7 +465,11 @@ void OverlapImpl::run_fused(int comm, const at::Tensor& A, const at::Tensor& B, 
     } else {
       // The caller's tensor is ordinary device memory that peers cannot address: reduce into
       // a symmetric buffer and copy.  Allocate outputs with symm_empty to avoid the copy.
-      if (out_ == nullptr || out_->bytes < out_bytes) out_ = heap_->allocate(out_bytes, stream());
+      if (out_ == nullptr || out_->bytes < out_bytes) {
+        SymmetricRegion* old = out_;
+        out_ = heap_->allocate(out_bytes, stream());
+        if (old != nullptr) heap_->release(old, stream());
+      }
       for (int r = 0; r < world_; ++r) p.dst[r] = out_->ptr[r];
       copy_back = true;
     }
@@ -503,6 +513,15 @@ void OverlapImpl::run_fused(int comm, const at::Tensor& A, const at::Tensor& B, 
     if (!norm_cnt_.defined() || norm_cnt_.numel() < p.tiles_m) norm_cnt_ = at::zeros({p.tiles_m}, i32);
     p.norm_w = norm_w->data_ptr();
     p.norm_eps = static_cast<float>(norm_eps);
+    if (norm_res != nullptr) {
+      check_out(*norm_res, A, static_cast<int64_t>(out_bytes / 2), "R");
+      p.norm_res[rank_] = norm_res->data_ptr();
+    }
+    if (norm_out != nullptr) {
+      check_out(*norm_out, A, static_cast<int64_t>(out_bytes / 2), "Y");
+      FO_CHECK(norm_out->data_ptr() != out.data_ptr(), "Y must not alias the residual stream");
+      p.norm_out[rank_] = norm_out->data_ptr();
+    }
     p.row_ssq = norm_ssq_.data_ptr<float>();
     p.panel_cnt = norm_cnt_.data_ptr<int>();
   }
@@ -580,6 +599,30 @@ void OverlapImpl::GemmReduceScatterRmsNormFused(at::Tensor A, at::Tensor B, at::
             static_cast<int>(Algo), &W, eps);
 }
 
+void OverlapImpl::GemmReduceScatterAddRmsNormFused(at::Tensor A, at::Tensor B, at::Tensor R, at::Tensor Y,
+                                                   at::Tensor W, double eps, int64_t Algo) {
+  NvtxRange nvtx_range("flashoverlap::gemm_reducescatter_add_rmsnorm_fused");
+  FO_CHECK(heap_ != nullptr, "call nccl_init first");
+  if (world_ == 1) {
+    // One rank: nothing to reduce; GEMM, residual add, then the stand-alone RMSNorm.
+    const GemmShape s = check_operands(A, B);
+    FO_CHECK(W.is_cuda() && W.is_contiguous() && W.scalar_type() == A.scalar_type() && W.numel() == s.N,
+             "W must be a contiguous CUDA tensor of N elements in the operands' dtype");
+    check_out(R, A, static_cast<int64_t>(s.M) * s.N, "R");
+    check_out(Y, A, static_cast<int64_t>(s.M) * s.N, "Y");
+    at::Tensor tmp = at::empty({s.M, s.N}, A.options());
+    Gemm(A, B, tmp, Algo);
+    at::Tensor r2 = R.view({s.M, s.N});
+    r2.add_(tmp);
+    cuda_check(rmsnorm_launch(r2.data_ptr(), Y.data_ptr(), W.data_ptr(), s.M, s.N, static_cast<float>(eps), s.bf16,
+                              sm_count_, stream()),
+               "rmsnorm");
+    return;
+  }
+  run_fused(kCommFusedRS, A, B, R, kOutNatural, nullptr, 1, nullptr, 0, false, nullptr, 0,
+            static_cast<int>(Algo), &W, eps, &R, &Y);
+}
+
 void OverlapImpl::GemmAll2AllFused(at::Tensor A, at::Tensor B, at::Tensor D, int64_t Algo,
                                    at::Tensor mLen_CPU) {
   NvtxRange nvtx_range("flashoverlap::gemm_all2all_fused");
@@ -614,7 +657,11 @@ void OverlapImpl::GemmAll2AllFused(at::Tensor A, at::Tensor B, at::Tensor D, int
     int64_t max_recv = 0;  // the scratch is one collective allocation: same size everywhere
     for (int r = 0; r < world_; ++r) max_recv = std::max(max_recv, all2all_plan(ml, world_, r).recv_rows);
     const size_t bytes = std::max<size_t>(static_cast<size_t>(max_recv) * p.N * 2, 256);
-    if (out_ == nullptr || out_->bytes < bytes) out_ = heap_->allocate(bytes, stream());
+    if (out_ == nullptr || out_->bytes < bytes) {
+      SymmetricRegion* old = out_;
+      out_ = heap_->allocate(bytes, stream());
+      if (old != nullptr) heap_->release(old, stream());
+    }
     for (int r = 0; r < world_; ++r) p.dst[r] = out_->ptr[r];
     copy_back = true;
   }

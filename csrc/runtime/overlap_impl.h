@@ -60,6 +60,12 @@ class OverlapImpl : public torch::CustomClassHolder {
   // over HBM.  Same arithmetic as reduce-scatter followed by `flashoverlap_op.rmsnorm`.
   void GemmReduceScatterRmsNormFused(at::Tensor A, at::Tensor B, at::Tensor Y, at::Tensor W, double eps,
                                      int64_t Algo);
+  // The same with the residual connection of a pre-norm transformer block in between:
+  //   R <- R + reduce_scatter(A * B^T)   (R [M / world, N]: the rank's rows of the residual stream, updated in place)
+  //   Y <- rmsnorm(R) * W
+  // i.e. what follows a sequence-parallel o_proj or down_proj, in the kernel that computes it.
+  void GemmReduceScatterAddRmsNormFused(at::Tensor A, at::Tensor B, at::Tensor R, at::Tensor Y, at::Tensor W,
+                                        double eps, int64_t Algo);
   // GEMM whose epilogue stores every row of A * B^T straight into the receive buffer D of the
   // rank it is bound for, over NVLink; same row bookkeeping as gemm_all2all (mLen_CPU[r][i]
   // rows go from rank r to rank i, runs packed in rank order, own run excluded), no C and no
@@ -137,7 +143,8 @@ class OverlapImpl : public torch::CustomClassHolder {
                  bool monitor, const int* cseg, int num_groups, int algo, int grid_cap);
   void run_fused(int comm, const at::Tensor& A, const at::Tensor& B, at::Tensor out, int out_mode,
                  const int* RA, int rldn, int* MM, int mm_stride, bool monitor, const int* cseg,
-                 int num_groups, int algo, const at::Tensor* norm_w = nullptr, double norm_eps = 0.0);
+                 int num_groups, int algo, const at::Tensor* norm_w = nullptr, double norm_eps = 0.0,
+                 const at::Tensor* norm_res = nullptr, const at::Tensor* norm_out = nullptr);
   void gated_overlap(int comm, at::Tensor A, at::Tensor B, at::Tensor C, at::Tensor D,
                      at::Tensor MM, at::Tensor RA, at::Tensor RE, int64_t rLDN,
                      at::Tensor cSEG_CPU, at::Tensor cSEG_GPU, int64_t Algo, bool monitor);
@@ -160,7 +167,7 @@ class OverlapImpl : public torch::CustomClassHolder {
   cudaEvent_t comm_done_ = nullptr;
   cudaEvent_t gemm_start_ = nullptr;
 
-  std::unique_ptr<SymmetricHeap> heap_;
+  std::shared_ptr<SymmetricHeap> heap_;  // shared with the tensors handed out by symm_empty
   SymmetricRegion* stage_ = nullptr;
   SymmetricRegion* signal_ = nullptr;
   SymmetricRegion* out_ = nullptr;  // symmetric AllReduce output when the caller's is not

@@ -40,6 +40,12 @@ CUDA_FLAGS = [
     "-lineinfo", "-O3", "-std=c++17",
     "--expt-relaxed-constexpr",
 ]
+# FLASHOVERLAP_DEBUG=1 in the environment of the build: the debug build, in which every overlap
+# call validates the values of its index arrays on the host before launching (option "validate"
+# defaults to 1).  The flag is part of the source hash, so switching it rebuilds.
+DEBUG_BUILD = os.environ.get("FLASHOVERLAP_DEBUG", "0") == "1"
+if DEBUG_BUILD:
+    CUDA_FLAGS = CUDA_FLAGS + ["-DFO_DEBUG=1"]
 
 _loaded = False
 
@@ -93,7 +99,7 @@ def _compile(verbose: bool = False) -> None:
     cpp_extension.load(
         name=_EXT_NAME,
         sources=[str(p) for p in _existing_sources()],
-        extra_cflags=["-O2", "-std=c++17"],
+        extra_cflags=["-O2", "-std=c++17"] + (["-DFO_DEBUG=1"] if DEBUG_BUILD else []),
         extra_cuda_cflags=CUDA_FLAGS,
         extra_include_paths=[str(_CSRC), nccl_inc],
         extra_ldflags=[f"-L{nccl_lib}", "-l:libnccl.so.2", f"-Wl,-rpath,{nccl_lib}"],

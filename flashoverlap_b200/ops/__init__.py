@@ -75,7 +75,9 @@ def fused_loopback(comm_op: str, A: List[torch.Tensor], B: List[torch.Tensor], o
                    timeout_ms: int = 1000, stage_local: bool = False,
                    mlen: Optional[torch.Tensor] = None, norm_w: Optional[torch.Tensor] = None,
                    norm_eps: float = 1e-5, trace: Optional[torch.Tensor] = None,
-                   epi_bufs: int = 2, pull_direct: bool = False) -> List[List[int]]:
+                   epi_bufs: int = 2, pull_direct: bool = False,
+                   norm_res: Optional[List[torch.Tensor]] = None,
+                   norm_out: Optional[List[torch.Tensor]] = None) -> List[List[int]]:
     """All ranks of a fused GEMM+collective on ONE GPU in one cooperative launch (test aid).
 
     ``stage_local`` selects the pull protocol: every rank stages its partial tiles in its own
@@ -87,7 +89,9 @@ def fused_loopback(comm_op: str, A: List[torch.Tensor], B: List[torch.Tensor], o
     ``trace`` (int64 CUDA tensor, ranks * tiles * 8) receives the per-tile timeline, see
     ``flashoverlap_b200.utils.trace``.  ``epi_bufs=4`` runs the build with four epilogue chunk buffers.
     ``pull_direct`` (with ``stage_local``): the epilogue threads store the partial tiles into the local
-    staging themselves instead of handing every chunk to the push warp's TMA stores."""
+    staging themselves instead of handing every chunk to the push warp's TMA stores.  ``norm_res`` /
+    ``norm_out`` (with ``norm_w``): per-rank residual added to the reduced rows before they are stored in
+    ``out[r]`` and normalised, and per-rank destination of the normalised rows (default: over ``out[r]``)."""
     flat = list(_op().fused_loopback(comm_op, A, B, out, RA, cseg, algo, strided_rows, natural_out, repeat,
-                                     timeout_ms, stage_local, mlen, norm_w, norm_eps, trace, epi_bufs, int(pull_direct)))
+                                     timeout_ms, stage_local, mlen, norm_w, norm_eps, trace, epi_bufs, int(pull_direct), norm_res, norm_out))
     return [flat[i:i + 8] for i in range(0, len(flat), 8)]

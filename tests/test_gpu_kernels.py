@@ -353,7 +353,8 @@ def test_overlap_call_rejects_short_index_arrays(cuda, impl):
     impl.check_status()
     impl.gemm_allreduce_overlap(a, b, c, mm, RA, 1, e, eg, algo, False)      # the object is still usable
     ref = a.float() @ b.float().t()
-    assert (c.float() - ref).abs().max().item() <= _tol(ref)
+    got = ops.unreorder(c, M, N, 128, 256, RA.reshape(tm, tn))
+    assert (got.float() - ref).abs().max().item() <= _tol(ref)
 
 
 def test_bad_ra_value_is_reported_not_followed(cuda):
@@ -474,3 +475,48 @@ def test_fused_loopback_pull_direct_stores(cuda, comm_op, ws, algo, strided):
         else:
             ref = full[layout.owned_rows(M, 128, ws, r, strided).to(cuda)]
         assert (out[r].float() - ref).abs().max().item() <= _tol(full), (comm_op, r)
+
+
+@pytest.mark.parametrize("ws,algo,strided,pull,direct", [(2, 0, True, False, False), (4, 2, False, True, False),
+                                                         (8, 0, True, True, True), (4, 0, True, False, False)])
+def test_reducescatter_residual_rmsnorm_tail_loopback(cuda, ws, algo, strided, pull, direct):
+    """R <- R + reduce_scatter(A B^T), Y <- rmsnorm(R) * w inside the fused kernel's reducers, with
+    either protocol: compared with the unfused arithmetic on 16-bit tensors."""
+    dt = torch.bfloat16
+    M, N, K = 1024, 2048, 192
+    A = [_rand((M, K), dt, cuda) for _ in range(ws)]
+    B = [_rand((N, K), dt, cuda) for _ in range(ws)]
+    w = (1 + 0.1 * torch.randn(N, device=cuda)).to(dt)
+    full = sum(a.float() @ b.float().t() for a, b in zip(A, B))
+    res0 = [_rand((M // ws, N), dt, cuda, 2.0) for _ in range(ws)]
+    R = [r.clone() for r in res0]
+    Y = [torch.full((M // ws, N), float("nan"), device=cuda, dtype=dt) for _ in range(ws)]
+    st = ops.fused_loopback("reduce_scatter", A, B, R, algo=algo, strided_rows=strided, natural_out=True,
+                            stage_local=pull, pull_direct=direct, norm_w=w, norm_eps=1e-5, norm_res=R, norm_out=Y)
+    assert all(s[0] == 0 for s in st), st
+    for r in range(ws):
+        rows = layout.owned_rows(M, 128, ws, r, strided).to(cuda)
+        h_ref = (res0[r].float() + full[rows].to(dt).float()).to(dt)
+        assert (R[r].float() - h_ref.float()).abs().max().item() <= _tol(full), r
+        y_ref = layout.rmsnorm_ref(R[r], w, 1e-5).float()
+        assert (Y[r].float() - y_ref).abs().max().item() <= 0.02 * y_ref.abs().max().item() + 1e-3, r
+
+
+@pytest.mark.parametrize("ws,algo", [(2, 0), (8, 2)])
+def test_reducescatter_rmsnorm_tail_pull_loopback(cuda, ws, algo):
+    """The RMSNorm tail with the pull protocol (partials staged locally, owners fetch them)."""
+    dt = torch.bfloat16
+    M, N, K = 1024, 1024, 192
+    A = [_rand((M, K), dt, cuda) for _ in range(ws)]
+    B = [_rand((N, K), dt, cuda) for _ in range(ws)]
+    w = (1 + 0.1 * torch.randn(N, device=cuda)).to(dt)
+    plain = [torch.empty(M // ws, N, device=cuda, dtype=dt) for _ in range(ws)]
+    st = ops.fused_loopback("reduce_scatter", A, B, plain, algo=algo, natural_out=True)
+    assert all(s[0] == 0 for s in st), st
+    Y = [torch.full((M // ws, N), float("nan"), device=cuda, dtype=dt) for _ in range(ws)]
+    st = ops.fused_loopback("reduce_scatter", A, B, Y, algo=algo, natural_out=True, stage_local=True, repeat=2,
+                            norm_w=w, norm_eps=1e-5)
+    assert all(s[0] == 0 for s in st), st
+    for r in range(ws):
+        y_ref = ops.rmsnorm(plain[r], w, 1e-5).float()
+        assert (Y[r].float() - y_ref).abs().max().item() <= 0.02 * y_ref.abs().max().item() + 1e-3, r

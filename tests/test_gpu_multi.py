@@ -204,6 +204,21 @@ def _norm_tail_worker(rank, world):
             impl.gemm_reducescatter_rmsnorm_fused(A, B, Y, w, 1e-5, algo)
         torch.cuda.synchronize(); dist.barrier()
         res[f"rs_norm_{algo}"] = (Y.float() - expect).abs().max().item() / (0.02 * expect.abs().max().item())
+        # with the residual of a pre-norm block in between, both protocols
+        for pull in (0, 1):
+            impl.set_option("stage_local", pull)
+            R0 = _rand((M // world, N), dev, 90 + rank, scale=2.0)
+            R = R0.clone()
+            Y2 = torch.full_like(D, float("nan"))
+            for _ in range(2):
+                R.copy_(R0)
+                impl.gemm_reducescatter_add_rmsnorm_fused(A, B, R, Y2, w, 1e-5, algo)
+            torch.cuda.synchronize(); dist.barrier()
+            h_ref = (R0.float() + D.float()).to(torch.bfloat16)
+            y_ref = ops.rmsnorm(h_ref, w, 1e-5).float()
+            res[f"rs_add_h_{algo}_{pull}"] = (R.float() - h_ref.float()).abs().max().item() / (0.02 * h_ref.float().abs().max().item())
+            res[f"rs_add_norm_{algo}_{pull}"] = (Y2.float() - y_ref).abs().max().item() / (0.02 * y_ref.abs().max().item())
+        impl.set_option("stage_local", 0)
     res["status"] = impl.read_status()[0]
     return res
 
