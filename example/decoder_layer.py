@@ -33,13 +33,29 @@ def worker(rank, world, args):
     g = torch.Generator(device="cpu").manual_seed(5)
     x_full = torch.randn(T, cfg.hidden, generator=g).to(torch.bfloat16).cuda()
     res, outs = {}, {}
-    for mode in ("nccl", "fused"):
-        layer = TPDecoderLayer(cfg, rank, world, batch, seq, impl=mode, overlap_impl=impl, algo=args.algo, seed=3)
+    if args.pull and world > 1:
+        # pull protocol of the fused kernels: staging with an NVSwitch multicast mapping, so the
+        # owners sum the partial tiles with one in-switch reduction per vector
+        from flashoverlap_b200.parallel import symm
+        symm.alloc_stage(impl, T, cfg.hidden, torch.bfloat16)
+        impl.set_option("stage_local", 1)
+    modes = [("nccl", "nccl", False), ("fused", "fused", False)] + ([("fused_norm_tail", "fused", True)] if world > 1 else [])
+    for name, mode, tail in modes:
+        layer = TPDecoderLayer(cfg, rank, world, batch, seq, impl=mode, overlap_impl=impl, algo=args.algo, seed=3,
+                               fuse_norm=tail)
         rows = layer.shard_rows().cuda()
         x_sp = x_full[rows].contiguous()
         with torch.no_grad():
             y = layer(x_sp)
-            res[mode] = perf_ms(lambda: layer(x_sp), args.warmup, args.reps)
+            res[name] = perf_ms(lambda: layer(x_sp), args.warmup, args.reps)
+            if not tail:
+                # the two row-parallel projections alone (GEMM + reduce-scatter), same operand shapes
+                attn = torch.randn(T, layer.q_local * cfg.head_dim, device="cuda").to(torch.bfloat16) * 0.1
+                act = torch.randn(T, layer.ffn_local, device="cuda").to(torch.bfloat16) * 0.1
+                res[name + "_o_proj"] = perf_ms(lambda: layer._row_parallel(attn, layer.wo), args.warmup, args.reps)
+                res[name + "_down_proj"] = perf_ms(lambda: layer._row_parallel(act, layer.wd), args.warmup, args.reps)
+                del attn, act
+        mode = name
         full = torch.zeros(T, cfg.hidden, device="cuda", dtype=torch.float32)
         full[rows] = y.float()
         if world > 1:
@@ -49,7 +65,13 @@ def worker(rank, world, args):
     impl.check_status()
     err = (outs["nccl"] - outs["fused"]).abs().max().item()
     scale = outs["nccl"].abs().max().item()
-    res.update(max_abs_diff=err, out_scale=scale, tokens=T, tp=world, speedup=res["nccl"] / res["fused"])
+    if "fused_norm_tail" in outs:
+        res["max_abs_diff_norm_tail"] = (outs["nccl"] - outs["fused_norm_tail"]).abs().max().item()
+        err = max(err, res["max_abs_diff_norm_tail"])
+    res.update(max_abs_diff=err, out_scale=scale, tokens=T, tp=world, speedup=res["nccl"] / res["fused"],
+               protocol="pull" if (args.pull and world > 1) else "push",
+               row_parallel_share_nccl=(res["nccl_o_proj"] + res["nccl_down_proj"]) / res["nccl"],
+               row_parallel_share_fused=(res["fused_o_proj"] + res["fused_down_proj"]) / res["fused"])
     if rank == 0:
         print(json.dumps({k: (round(v, 5) if isinstance(v, float) else v) for k, v in res.items()}))
     return err <= 0.03 * scale + 1e-2
@@ -61,6 +83,7 @@ def main():
     ap.add_argument("--seq", type=int, default=4096)
     ap.add_argument("--algo", type=int, default=1)
     ap.add_argument("--tiny", action="store_true")
+    ap.add_argument("--pull", action="store_true", help="fused kernels use the pull protocol (in-switch reduction)")
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--reps", type=int, default=10)
     args = ap.parse_args()

@@ -68,13 +68,16 @@ class TPDecoderLayer(nn.Module):
 
     def __init__(self, cfg: DecoderConfig, rank: int, world: int, batch: int, seq: int, impl: str = "fused",
                  overlap_impl=None, tp_group=None, dtype=torch.bfloat16, device="cuda", algo: int = 0,
-                 seed: int = 0):
+                 seed: int = 0, fuse_norm: bool = False):
         super().__init__()
         assert impl in ("fused", "nccl")
         assert cfg.n_heads % world == 0 and cfg.n_kv_heads % world == 0 and cfg.ffn % world == 0
         assert (batch * seq) % TILE_M == 0 and TILE_M % world == 0
         self.cfg, self.rank, self.world, self.batch, self.seq = cfg, rank, world, batch, seq
         self.impl, self.ov, self.group, self.algo = impl, overlap_impl, tp_group, algo
+        # impl="fused" only: o_proj's residual add and the RMSNorm that follows it run inside the
+        # reduce-scatter kernel's reducers (gemm_reducescatter_add_rmsnorm_fused)
+        self.fuse_norm = bool(fuse_norm) and impl == "fused" and world > 1
         if impl == "fused" and world > 1:
             assert overlap_impl is not None, "impl='fused' needs an OverlapImpl"
             overlap_impl.set_option("strided_rows", 0)  # contiguous blocks inside each tile
@@ -151,9 +154,17 @@ class TPDecoderLayer(nn.Module):
         q, k = _rope(q, cfg.rope_theta), _rope(k, cfg.rope_theta)
         attn = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)
         attn = attn.transpose(1, 2).reshape(B * S, self.q_local * hd)
-        h_sp = x_sp + self._row_parallel(attn, self.wo)                        # [T/tp, h]
+        if self.fuse_norm:
+            # h = x + reduce_scatter(attn @ wo^T) and rmsnorm(h) * w in the kernel that reduces
+            h_sp = x_sp.clone()
+            hn_sp = torch.empty_like(h_sp)
+            self.ov.gemm_reducescatter_add_rmsnorm_fused(attn.contiguous(), self.wo, h_sp, hn_sp, self.mlp_norm,
+                                                         cfg.eps, self.algo)
+            hn = self._all_gather_tokens(hn_sp)
+        else:
+            h_sp = x_sp + self._row_parallel(attn, self.wo)                    # [T/tp, h]
+            hn = self._all_gather_tokens(self._norm(h_sp, self.mlp_norm))
         # MLP block
-        hn = self._all_gather_tokens(self._norm(h_sp, self.mlp_norm))
         gu = torch.matmul(hn, self.wgu.t())
         gate, up = gu.split([self.ffn_local, self.ffn_local], dim=-1)
         act = F.silu(gate) * up

@@ -325,16 +325,16 @@ def _layer_worker(rank, world):
     T = batch * seq
     x_full = _rand((T, cfg.hidden), dev, 7, scale=1.0)
     outs = {}
-    for mode in ("nccl", "fused"):
-        layer = TPDecoderLayer(cfg, rank, world, batch, seq, impl=mode, overlap_impl=impl, seed=3)
+    for name, mode, tail in (("nccl", "nccl", False), ("fused", "fused", False), ("fused_tail", "fused", True)):
+        layer = TPDecoderLayer(cfg, rank, world, batch, seq, impl=mode, overlap_impl=impl, seed=3, fuse_norm=tail)
         rows = layer.shard_rows().to(dev)
         y = layer(x_full[rows])
         full = torch.zeros(T, cfg.hidden, device=dev, dtype=torch.float32)
         full[rows] = y.float()
         dist.all_reduce(full)
-        outs[mode] = full
+        outs[name] = full
     torch.cuda.synchronize()
-    err = (outs["nccl"] - outs["fused"]).abs().max().item()
+    err = max((outs["nccl"] - outs["fused"]).abs().max().item(), (outs["nccl"] - outs["fused_tail"]).abs().max().item())
     return {"err": err, "scale": outs["nccl"].abs().max().item(), "status": impl.read_status()[0]}
 
 
