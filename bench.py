@@ -35,7 +35,7 @@ M_RS, N_RS, K_RS_TOTAL = 16384, 8192, 8192
 # while the board's power management was still settling under the 1 kW cap.
 WARM_SECONDS = 1.0
 CHECK_ROWS_PER_PANEL = 8     # rows of every 128-row panel compared with the fp32 reference
-TIMED_BLOCKS = 5             # blocks of `steps` steps; the median block is the reported one
+TIMED_BLOCKS = 9             # blocks of `steps` steps; the median block is the reported one
 NVLINK_GBS = 770.0           # measured peer-copy bandwidth per direction per GPU (B200, NVLink 5)
 REAL_STDOUT = sys.stdout
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
