@@ -116,41 +116,36 @@ class ClockSampler:
         return out
 
 
-def pick_algo(torch, dist, world, run, candidates, flush, reps=10, settle_seconds=WARM_SECONDS, check=None):
-    """Fastest Algo by a short timing, agreed on by all ranks (max over ranks per candidate).
-    The candidates are ranked in the regime of the timed region: after the same settling time
-    under load (a cold GPU runs all of them at boost clocks, while the timed region runs at the
-    power cap, where the kernels that move fewer bytes win), with the L2 flushed between calls
-    and per-call events."""
-    try:
-        run(candidates[0])
-        torch.cuda.synchronize()
-        t0 = time.perf_counter()
-        run(candidates[0])
-        flush()
-        torch.cuda.synchronize()
-        one = torch.tensor([max(time.perf_counter() - t0, 1e-5)], device="cuda")
-        if world > 1:
-            dist.all_reduce(one, op=dist.ReduceOp.MAX)       # same number of settling steps on every rank
-        for _ in range(int(min(2000, settle_seconds / one.item()))):
-            run(candidates[0])
-            flush()
-    except Exception:
-        pass
+def pick_algo(torch, dist, world, run, candidates, flush, reps=10, settle_seconds=0.35, check=None):
+    """Fastest candidate, agreed on by all ranks (max over ranks per candidate).
+
+    Every candidate is ranked in the regime of the timed region - under ITS OWN sustained load.
+    The board runs at its 1 kW cap in the timed region, and the kernels differ in the power they
+    draw per FLOP (operand bytes per FLOP, mostly), so the clock each one sustains is part of its
+    time: a kernel that wins a short burst after another kernel's warm-up can lose by 10 % once the
+    power controller has settled on it.  So each candidate first runs alone for `settle_seconds`,
+    then is timed with per-call events and the L2 flushed between calls."""
     times = []
     for a in candidates:
         try:
             run(a)
-            if check is not None:
+            torch.cuda.synchronize()
+            if check is not None and not check():
                 # a candidate whose device-side waits give up is dropped after ONE call instead of
                 # running into its time limit on every timed iteration
-                torch.cuda.synchronize()
-                if not check():
-                    raise RuntimeError("device status not ok")
-            for _ in range(2):
+                raise RuntimeError("device status not ok")
+            t0 = time.perf_counter()
+            run(a)
+            flush()
+            torch.cuda.synchronize()
+            one = torch.tensor([max(time.perf_counter() - t0, 1e-5)], device="cuda")
+            if world > 1:
+                dist.all_reduce(one, op=dist.ReduceOp.MAX)       # same number of settling steps on every rank
+            for _ in range(int(min(2000, settle_seconds / one.item()))):
                 run(a)
                 flush()
-            ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(reps)]
+            n = max(reps, int(min(400, 0.15 / one.item())))
+            ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(n)]
             torch.cuda.synchronize()
             if world > 1:
                 dist.barrier()
@@ -160,7 +155,7 @@ def pick_algo(torch, dist, world, run, candidates, flush, reps=10, settle_second
                 run(a)
                 e.record()
             torch.cuda.synchronize()
-            times.append(sum(s.elapsed_time(e) for s, e in ev) / reps)
+            times.append(sum(s.elapsed_time(e) for s, e in ev) / n)
         except Exception:
             times.append(1e9)
     t = torch.tensor(times, device="cuda")
@@ -550,7 +545,7 @@ def extras(torch, dist, impl, rank, world, dev, A, B, C, algo, flush, peaks, ste
     rs_cands = [(a, pr, "norm_kernel") for pr in rs_protocols for a in (0, 1, 3)]
     if world > 1:
         rs_cands += [(a, "push", "tail") for a in (0, 1)]
-    rs_cand, rs_probe = pick_algo(torch, dist, world, rs_step, rs_cands, flush, settle_seconds=0.3, check=healthy)
+    rs_cand, rs_probe = pick_algo(torch, dist, world, rs_step, rs_cands, flush, settle_seconds=0.2, check=healthy)
     ms, _, _ = time_steps(torch, dist, world, lambda: rs_step(rs_cand), steps, warm, flush)
     if world > 1:
         impl.set_option("stage_local", 1 if protocol == "pull" else 0)

@@ -117,6 +117,10 @@ struct GemmParams {
   // (row-major [M, N], or the tile-contiguous layout as [M * N / (rldn * BN), rldn * BN]) and
   // finished chunks leave shared memory as TMA tensor stores; 0 = per-thread 16-byte stores.
   int tma_out;
+  // Back-off of the roles that wait on mbarriers with slack (TMA producer, MMA issuer, push warp;
+  // four times as long for the epilogue's wait for its accumulator): nanoseconds slept between
+  // polls once a wait has turned out to be a long one.  0 = poll continuously.
+  uint32_t wait_sleep_ns;
 };
 
 constexpr int kTraceSlots = 8;

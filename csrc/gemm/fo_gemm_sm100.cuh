@@ -538,7 +538,7 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
       for (int pos = unit; ok && pos < sched_tiles; pos += num_units) {
         const TileCoord tc = my_tile(pos);
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!ptx::mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, s_abort, pipe_timeout)) {
+          if (!ptx::mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, s_abort, pipe_timeout, p.wait_sleep_ns)) {
             ptx::report_status(status, kStatusTimeoutSmemEmpty, pos, kb, stage);
             *s_abort = 1;
             ok = false;
@@ -592,7 +592,7 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
       uint32_t acc_phase = 0;
       bool ok = true;
       for (int pos = unit; ok && pos < sched_tiles; pos += num_units) {
-        if (!ptx::mbar_wait_bounded(&tmem_empty_bar[acc], acc_phase ^ 1u, s_abort, pipe_timeout)) {
+        if (!ptx::mbar_wait_bounded(&tmem_empty_bar[acc], acc_phase ^ 1u, s_abort, pipe_timeout, p.wait_sleep_ns)) {
           ptx::report_status(status, kStatusTimeoutTmemEmpty, pos, acc, 0);
           *s_abort = 1;
           break;
@@ -600,7 +600,7 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
         ptx::tc_fence_after_sync();
         const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(acc * BN);
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!ptx::mbar_wait_bounded(&full_bar[stage], phase, s_abort, pipe_timeout)) {
+          if (!ptx::mbar_wait_bounded(&full_bar[stage], phase, s_abort, pipe_timeout, p.wait_sleep_ns)) {
             ptx::report_status(status, kStatusTimeoutSmemFull, pos, kb, stage);
             *s_abort = 1;
             ok = false;
@@ -721,7 +721,7 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
       const TileCoord tc0 = my_tile(pos);
 
       if (et == 0) {
-        int ok = ptx::mbar_wait_bounded(&tmem_full_bar[acc], acc_phase, s_abort, pipe_timeout) ? 1 : 0;
+        int ok = ptx::mbar_wait_bounded(&tmem_full_bar[acc], acc_phase, s_abort, pipe_timeout, 4u * p.wait_sleep_ns) ? 1 : 0;
         if (!ok) {
           ptx::report_status(status, kStatusTimeoutTmemFull, pos, acc, 0);
           *s_abort = 1;
@@ -1119,7 +1119,7 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
           if (p.stage_local != 0 && p.pull_direct != 0) {
             // The epilogue threads stored the tile into the local staging themselves; announce it.
             const int b = static_cast<int>(chunk_no % EPI);
-            if (!ptx::mbar_wait_bounded(&chunk_ready_bar[b], (chunk_no / EPI) & 1u, s_abort, pipe_timeout)) {
+            if (!ptx::mbar_wait_bounded(&chunk_ready_bar[b], (chunk_no / EPI) & 1u, s_abort, pipe_timeout, p.wait_sleep_ns)) {
               ptx::report_status(status, kStatusTimeoutTmemFull, pos, 0, 2);
               *s_abort = 1;
               ok = false;
@@ -1136,7 +1136,7 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
           }
           for (int c = 0; c < kChunks; ++c, ++chunk_no) {
             const int b = static_cast<int>(chunk_no % EPI);
-            if (!ptx::mbar_wait_bounded(&chunk_ready_bar[b], (chunk_no / EPI) & 1u, s_abort, pipe_timeout)) {
+            if (!ptx::mbar_wait_bounded(&chunk_ready_bar[b], (chunk_no / EPI) & 1u, s_abort, pipe_timeout, p.wait_sleep_ns)) {
               ptx::report_status(status, kStatusTimeoutTmemFull, pos, c, 1);
               *s_abort = 1;
               ok = false;

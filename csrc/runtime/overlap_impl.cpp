@@ -108,6 +108,9 @@ void OverlapImpl::SetOption(std::string name, int64_t value) {
   } else if (name == "pull_direct") {
     FO_CHECK(value >= -1 && value <= 1, "pull_direct must be -1 (automatic), 0 or 1");
     opt_pull_direct_ = value;
+  } else if (name == "wait_sleep_ns") {
+    FO_CHECK(value >= 0 && value <= 10000, "wait_sleep_ns must be in [0, 10000]");
+    opt_wait_sleep_ns_ = value;
   } else if (name == "validate") {
     opt_validate_ = value ? 1 : 0;
   } else if (name == "tma_out") {
@@ -133,6 +136,7 @@ int64_t OverlapImpl::GetOption(std::string name) {
   if (name == "epi_bufs") return opt_epi_bufs_;
   if (name == "tma_out") return opt_tma_out_;
   if (name == "validate") return opt_validate_;
+  if (name == "wait_sleep_ns") return opt_wait_sleep_ns_;
   if (name == "pull_direct") return opt_pull_direct_;
   if (name == "diag") return opt_diag_;
   if (name == "sm_count") return sm_count_;
@@ -290,6 +294,7 @@ void OverlapImpl::run_plain(const at::Tensor& A, const at::Tensor& B, void* out,
   p.ws = 1;
   p.rank_base = rank_;
   p.timeout_ns = static_cast<uint64_t>(opt_timeout_ms_) * 1000000ull;
+  p.wait_sleep_ns = static_cast<uint32_t>(opt_wait_sleep_ns_);
   p.RA = RA;
   p.RE = RE;
   p.cseg = cseg;
@@ -495,6 +500,7 @@ void OverlapImpl::run_fused(int comm, const at::Tensor& A, const at::Tensor& B, 
   p.epoch_done_prev = static_cast<uint32_t>(world_) * (epoch - 1);
   p.epoch_done = static_cast<uint32_t>(world_) * epoch;
   p.timeout_ns = static_cast<uint64_t>(opt_timeout_ms_) * 1000000ull;
+  p.wait_sleep_ns = static_cast<uint32_t>(opt_wait_sleep_ns_);
   p.RA = RA;
   p.cseg = cseg;
   p.MM[0] = MM;
@@ -683,6 +689,7 @@ void OverlapImpl::GemmAll2AllFused(at::Tensor A, at::Tensor B, at::Tensor D, int
   p.epoch_done = static_cast<uint32_t>(world_) * (epoch_ + 1);
   p.epoch_ready = static_cast<uint32_t>(world_) * (a2a_epoch_ + 1);
   p.timeout_ns = static_cast<uint64_t>(opt_timeout_ms_) * 1000000ull;
+  p.wait_sleep_ns = static_cast<uint32_t>(opt_wait_sleep_ns_);
   p.a2a_tab = a2a_tab_.data_ptr<int>();
   p.status[0] = status_.data_ptr<int>();
   p.local_cnt[0] =
