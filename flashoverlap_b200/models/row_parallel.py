@@ -47,11 +47,16 @@ class OverlapRowParallelLayer(nn.Module):
         by :class:`ReorderRMSNorm`;
       * ``"natural"``: row-major output written directly by the fused kernel (no reorder pass is
         needed at all, because the in-kernel collective does not require contiguous ranges).
+
+    ``protocol`` (fused mode, several ranks): ``"push"`` - partial tiles are stored into the owning
+    ranks' staging buffers - or ``"pull"`` - they stay in this rank's staging buffer, allocated
+    here with an NVSwitch multicast mapping when torch can provide one, and the owners sum them
+    with one in-switch reduction per vector (``multimem.ld_reduce``).
     """
 
     def __init__(self, rank: int, world_size: int, in_features: int, out_features: int, M: int,
                  config: dict, comm_op: str, nccl_id, dtype=torch.bfloat16, layout_mode: str = "reordered",
-                 impl=None, mode: str = "fused"):
+                 impl=None, mode: str = "fused", protocol: str = "push"):
         super().__init__()
         if comm_op not in ("all_reduce", "reduce_scatter"):
             raise ValueError(f"comm_op must be 'all_reduce' or 'reduce_scatter', got {comm_op!r}")
@@ -87,6 +92,14 @@ class OverlapRowParallelLayer(nn.Module):
             from ..parallel import symm
             self._out, self.uses_multicast = symm.alloc_allreduce_output(impl, (M, out_features), dtype)
         self._tmp = None
+        if protocol not in ("push", "pull"):
+            raise ValueError(f"protocol must be 'push' or 'pull', got {protocol!r}")
+        self.protocol = protocol if (world_size > 1 and mode == "fused") else "push"
+        if self.protocol == "pull":
+            from ..parallel import symm
+            self._stage, self.stage_multicast = symm.alloc_stage(impl, M, out_features, dtype)
+        if world_size > 1 and mode == "fused":
+            impl.set_option("stage_local", 1 if self.protocol == "pull" else 0)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         N = self.weight.size(0)

@@ -10,12 +10,6 @@ def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (B200); run with -m gpu")
 
 
-# Features whose GPU tests have not yet passed on hardware are built and kept out of the default
-# run; FLASHOVERLAP_EXPERIMENTAL=1 includes them.
-experimental = pytest.mark.skipif(os.environ.get("FLASHOVERLAP_EXPERIMENTAL", "0") != "1",
-                                  reason="set FLASHOVERLAP_EXPERIMENTAL=1 to run tests of not yet validated features")
-
-
 @pytest.fixture(scope="session")
 def lib():
     """Loads the native extension; GPU tests must run native code, never a fallback."""
