@@ -146,7 +146,7 @@ std::vector<int64_t> fused_loopback(std::string comm_op, std::vector<at::Tensor>
   }
   if (const char* d = std::getenv("FLASHOVERLAP_DIAG")) p.diag = std::atoi(d);  // timing studies only
   p.timeout_ns = static_cast<uint64_t>(timeout_ms) * 1000000ull;
-  p.wait_sleep_ns = 64;
+  p.wait_sleep_ns = 0;
   p.RA = int_ptr_or_null(RA, "RA");
   p.cseg = cseg;
   for (int r = 0; r < ws; ++r) {

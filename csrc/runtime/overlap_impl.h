@@ -86,8 +86,8 @@ class OverlapImpl : public torch::CustomClassHolder {
   // warp's TMA stores, -1, the default: direct for the 256 x 256-per-CTA kernels),
   // "epi_bufs" (2 | 4: fused kernels with four epilogue chunk buffers and one operand stage fewer;
   // their push warp keeps three chunks of stores in flight instead of waiting for each),
-  // "wait_sleep_ns" (nanoseconds the kernel's waiting roles sleep between mbarrier polls; 0 = poll
-  // continuously),
+  // "wait_sleep_ns" (nanoseconds the kernel's waiting roles sleep between mbarrier polls; 0, the
+  // default = poll continuously: 64 and 256 ns changed neither the instruction count nor the time),
   // "validate" (1: overlap calls also check the values of RA / RE / cSEG_GPU - permutation, range,
   // sum - at the price of a device-to-host copy per call; on by default in a -DFO_DEBUG build),
   // "tma_out" (1: plain GEMMs with a row-major or tile-contiguous output store finished chunks
@@ -197,7 +197,7 @@ class OverlapImpl : public torch::CustomClassHolder {
 #endif
   int64_t opt_tma_out_ = -1;     // plain kernels' stores: 1 TMA tensor stores, 0 per-thread stores, -1 by kernel
   int64_t opt_pull_direct_ = -1;  // pull protocol: epilogue threads store the partials themselves (1), TMA (0), by kernel (-1)
-  int64_t opt_wait_sleep_ns_ = 64;  // back-off of the kernel roles that wait with slack (0: poll continuously)
+  int64_t opt_wait_sleep_ns_ = 0;   // back-off of the kernel roles that wait with slack (0: poll continuously; measured: no gain)
   int64_t opt_stage_local_ = 0;  // 1: pull protocol (partials staged locally, owners fetch them)
   int64_t opt_l2_hints_ = 0;  // measured: priorities raise DRAM traffic on B200, off by default
 };
