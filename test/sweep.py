@@ -51,6 +51,12 @@ def worker(rank, world, args):
                     # a fresh runtime object per case: its symmetric memory is released with it
                     impl = bootstrap.make_overlap_impl(rank, world)
                     impl.set_option("timeout_ms", 20000)
+                    if getattr(args, "pull", False) and world > 1:
+                        # pull protocol: partials staged locally, summed by the switch when the
+                        # staging buffer gets a multicast mapping
+                        from flashoverlap_b200.parallel import symm
+                        symm.alloc_stage(impl, M, N, dt)
+                        impl.set_option("stage_local", 1)
                     sm, margin = impl.get_option("sm_count"), impl.get_option("sm_margin")
                     best = None
                     for algo in ((19, 17, 1) if M % 512 == 0 else ((1, 17) if M % 256 == 0 else (0, 16))):
@@ -70,6 +76,7 @@ def worker(rank, world, args):
                     gemm_ms = perf_ms(lambda: impl.cutlass_gemm(wl.A, wl.B, full, algo), args.warmup, args.reps, args.flush)
                     roof = tuner.roofline_ms(M, N, K, world, comm_op, peaks["bf16_tflops"], 770.0)
                     rec = {"comm_op": comm_op, "M": M, "N": N, "K_total": Kt, "tp": world, "Algo": algo,
+                           "protocol": "pull" if (getattr(args, "pull", False) and world > 1) else "push",
                            "fused_ms": round(fused_ms, 5), "cublas_nccl_ms": round(base_ms, 5), "gemm_ms": round(gemm_ms, 5),
                            "speedup": round(base_ms / fused_ms, 4), "roofline_ms": round(roof, 5),
                            "roofline_frac": round(roof / fused_ms, 4)}
@@ -132,6 +139,7 @@ def main():
     ap.add_argument("--quick", action="store_true")
     ap.add_argument("--groupings", action="store_true", help="also search the gated mechanism's wave groupings")
     ap.add_argument("--flush", action="store_true")
+    ap.add_argument("--pull", action="store_true", help="fused kernels use the pull protocol (in-switch reduction)")
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--reps", type=int, default=20)
     ap.add_argument("--path", default=None)
