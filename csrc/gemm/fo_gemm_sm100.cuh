@@ -22,9 +22,13 @@
 //               128-byte coalesced global (local or peer) stores, then the signal;
 //   warps 6-9   (fused only) reducer for the row slices this rank owns;
 //   warp 10     (fused only) push: one thread turns every finished shared-memory chunk into TMA
-//               stores to the owning ranks' staging memory and, once a tile's stores have
-//               completed, bumps the owners' arrival counters.  Waiting for remote completion
-//               happens here, off the epilogue's critical path.
+//               stores to the owning ranks' staging memory (or this rank's own, pull protocol)
+//               and, once a tile's stores have completed, hands the tile to the signal warp.
+//               Waiting for remote completion happens here, off the epilogue's critical path;
+//   warp 11     (fused only) signal: one thread publishes finished tiles - a system-scope
+//               release fence, then relaxed atomics on the owners' arrival counters.  The fence
+//               waits for every remote write the SM has in flight, which is why it has a warp
+//               of its own: on the push warp it stalled the epilogue for a whole tile period.
 // The two TMEM accumulators let tile i's epilogue run under tile i+1's main loop.
 //
 // CTA2 variant: two CTAs of a cluster (adjacent SMs) share one 256 x 256 tile through
@@ -63,6 +67,10 @@
 
 namespace fo {
 
+// Tiles that the push warp may have handed to the signal warp without their arrival having been
+// announced yet (fused kernels).
+constexpr int kSigRing = 4;
+
 template <int BN, int STAGES, bool CTA2 = false, int MT = 1, int EPI = 2>
 struct GemmSmem {
   static constexpr int kAHalfBytes = kBM * kBK * 2;
@@ -74,7 +82,8 @@ struct GemmSmem {
   static constexpr int kRingBytes = STAGES * kStageBytes;
   static constexpr int kEpiOffset = kRingBytes;
   static constexpr int kBarOffset = kEpiOffset + EPI * kEpiBufBytes;  // EPI epilogue chunk buffers
-  static constexpr int kNumBars = 2 * STAGES + 4 + 2 * EPI;  // + chunk_ready[EPI], chunk_free[EPI]
+  // + chunk_ready[EPI], chunk_free[EPI], sig_full[kSigRing], sig_empty[kSigRing]
+  static constexpr int kNumBars = 2 * STAGES + 4 + 2 * EPI + 2 * kSigRing;
   static constexpr int kMiscOffset = kBarOffset + kNumBars * 8;
   static constexpr int kMiscBytes = 64;
   // +1024: the ring is aligned up to 1024 B at run time (128-byte swizzle atom).
@@ -134,7 +143,7 @@ __device__ __forceinline__ int tile_position(const GemmParams& p, int t, int32_t
 constexpr int kEpilogueThreads = 128;
 constexpr int kReducerThreads = 128;
 constexpr int kThreadsPlain = 64 + kEpilogueThreads;
-constexpr int kThreadsFused = kThreadsPlain + kReducerThreads + 32;  // + push warp
+constexpr int kThreadsFused = kThreadsPlain + kReducerThreads + 64;  // + push warp + signal warp
 
 template <bool BF16>
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
@@ -451,6 +460,8 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
   uint64_t* tmem_empty_bar = bars + 2 * STAGES + 2;
   uint64_t* chunk_ready_bar = bars + 2 * STAGES + 4;  // epilogue -> push warp: chunk written
   uint64_t* chunk_free_bar = chunk_ready_bar + EPI;   // push warp -> epilogue: chunk buffer reusable
+  uint64_t* sig_full_bar = chunk_free_bar + EPI;      // push warp -> signal warp: a tile's stores have landed
+  uint64_t* sig_empty_bar = sig_full_bar + kSigRing;  // signal warp -> push warp: ring slot reusable
   uint32_t* misc = reinterpret_cast<uint32_t*>(smem + L::kMiscOffset);
   uint32_t* s_tmem_base = misc;                                   // written by tcgen05.alloc
   volatile int* s_abort = reinterpret_cast<volatile int*>(misc + 1);
@@ -458,6 +469,9 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
   volatile int* s_is_last = reinterpret_cast<volatile int*>(misc + 3);
   // two slots, alternated per tile: a slow reader of tile i never sees tile i+1's verdict
   volatile int* s_red_ok = reinterpret_cast<volatile int*>(misc + 4);
+  // ring between the push warp and the signal warp: wave group and tile id of each handed-over tile
+  volatile int* s_sig_g = reinterpret_cast<volatile int*>(misc + 8);
+  volatile int* s_sig_t = reinterpret_cast<volatile int*>(misc + 12);
 
   const int warp_idx = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -496,6 +510,10 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
     for (int i = 0; i < EPI; ++i) {
       ptx::mbar_init(&chunk_ready_bar[i], kEpilogueThreads);
       ptx::mbar_init(&chunk_free_bar[i], 1);
+    }
+    for (int i = 0; i < kSigRing; ++i) {
+      ptx::mbar_init(&sig_full_bar[i], 1);
+      ptx::mbar_init(&sig_empty_bar[i], 1);
     }
     *s_abort = 0;
     *s_ep_ok = 1;
@@ -1074,7 +1092,7 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
         }
       }
     }
-  } else {
+  } else if (warp_idx == 10) {
     // ------------------------------------------------------------------ push warp (fused)
     if constexpr (FUSED) {
       if (lane == 0) {
@@ -1082,19 +1100,32 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
         constexpr int kMaxLag = 4;
         const int rows_owned = kBM / p.ws;
         const uint8_t* epi = smem + L::kEpiOffset;
-        const int lag = p.push_lag < 1 ? 1 : (p.push_lag > kMaxLag ? kMaxLag : p.push_lag);
+        // Tiles of stores kept in flight before the oldest one's completion is awaited.  Stores
+        // into the local staging (pull protocol) complete within a microsecond or two: no lag.
+        const int lag = p.stage_local ? 0 : (p.push_lag < 1 ? 1 : (p.push_lag > kMaxLag ? kMaxLag : p.push_lag));
         int ring[kMaxLag];       // wave groups of the tiles whose pushes may still be in flight
-        int ring_t[TRACE ? kMaxLag : 1];  // their tile ids (tracing builds only)
+        int ring_t[kMaxLag];     // their tile ids
         int ring_head = 0, ring_count = 0;
         uint32_t chunk_no = 0;
+        uint32_t sig_no = 0;     // tiles handed to the signal warp
         bool ok = true;
 
-        auto signal_group = [&](int g) {
-          // The tile's stores have completed (bulk wait); publish that to the owners.
-          // One release fence, then a batch of relaxed atomics that travel concurrently.
-          ptx::fence_proxy_async_all();
-          ptx::fence_acq_rel_sys();
-          for (int o = 0; o < p.ws; ++o) ptx::red_relaxed_sys_add(p.flags[(me + o) % p.ws] + g, 1u);
+        // A tile's stores have completed (bulk wait): hand it to the signal warp, which
+        // publishes it to the owners.  The system-scope release fence that publication needs
+        // waits for every remote write this SM has in flight - tens of microseconds once the
+        // reducers are storing results through the switch - and the chunk buffers give the
+        // epilogue only two chunks of slack, so it must not run on this thread.
+        auto signal_group = [&](int g, int t) {
+          const uint32_t slot = sig_no % kSigRing;
+          if (!ptx::mbar_wait_bounded(&sig_empty_bar[slot], ((sig_no / kSigRing) & 1u) ^ 1u, s_abort, pipe_timeout)) {
+            *s_abort = 1;
+            return;
+          }
+          s_sig_g[slot] = g;
+          s_sig_t[slot] = t;
+          ptx::fence_proxy_async_all();          // the bulk stores before the hand-over
+          ptx::mbar_arrive(&sig_full_bar[slot]);  // release at CTA scope
+          ++sig_no;
         };
 
         // Peers may still be reading the staging slices of the previous call.
@@ -1128,8 +1159,7 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
             stamp(t, kTracePushIssued);
             int g, need;
             group_of_position(p, r, &g, &need);
-            signal_group(g);
-            stamp(t, kTraceSignalled);
+            signal_group(g, t);
             ptx::mbar_arrive(&chunk_free_bar[b]);
             ++chunk_no;
             continue;
@@ -1169,6 +1199,11 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
           stamp(t, kTracePushIssued);
           int g, need;
           group_of_position(p, r, &g, &need);
+          if (lag == 0) {
+            ptx::bulk_wait_group<0>();
+            signal_group(g, t);
+            continue;
+          }
           if (ring_count == lag) {
             // The oldest tile in flight was issued `lag` tiles ago; with a main loop between
             // tiles its stores have long completed and this wait returns at once.
@@ -1178,23 +1213,52 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
               case 3: ptx::bulk_wait_group<kChunks * 3>(); break;
               default: ptx::bulk_wait_group<kChunks * 4>(); break;
             }
-            signal_group(ring[ring_head]);
-            if constexpr (TRACE) stamp(ring_t[ring_head], kTraceSignalled);
+            signal_group(ring[ring_head], ring_t[ring_head]);
             ring_head = (ring_head + 1) % kMaxLag;
             --ring_count;
           }
           ring[(ring_head + ring_count) % kMaxLag] = g;
-          if constexpr (TRACE) ring_t[(ring_head + ring_count) % kMaxLag] = t;
+          ring_t[(ring_head + ring_count) % kMaxLag] = t;
           ++ring_count;
         }
         // Flush: every push must have landed before it is announced, and no bulk copy may
         // still read this CTA's shared memory when it exits.
         ptx::bulk_wait_group<0>();
         while (ring_count > 0) {
-          signal_group(ring[ring_head]);
-          if constexpr (TRACE) stamp(ring_t[ring_head], kTraceSignalled);
+          signal_group(ring[ring_head], ring_t[ring_head]);
           ring_head = (ring_head + 1) % kMaxLag;
           --ring_count;
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ signal warp (fused)
+    // Publishes finished tiles to their owners: ONE system-scope release fence for every tile
+    // that is waiting in the ring, then a batch of relaxed atomics on the owners' arrival
+    // counters that travel concurrently.  (A chain of red.release.sys would make every atomic
+    // wait for the previous one's NVLink round trip.)
+    if constexpr (FUSED) {
+      if (lane == 0) {
+        uint32_t total = 0;  // tiles this CTA computes
+        for (int pos = unit; pos < sched_tiles; pos += num_units) total += MT;
+        uint32_t n = 0;
+        while (n < total) {
+          if (!ptx::mbar_wait_bounded(&sig_full_bar[n % kSigRing], (n / kSigRing) & 1u, s_abort, pipe_timeout)) break;
+          uint32_t m = 1;  // further tiles that are already waiting share the fence
+          while (n + m < total && m < static_cast<uint32_t>(kSigRing) &&
+                 ptx::mbar_try_wait(&sig_full_bar[(n + m) % kSigRing], ((n + m) / kSigRing) & 1u)) {
+            ++m;
+          }
+          ptx::fence_proxy_async_all();
+          ptx::fence_acq_rel_sys();
+          for (uint32_t j = 0; j < m; ++j) {
+            const uint32_t slot = (n + j) % kSigRing;
+            const int g = s_sig_g[slot];
+            for (int o = 0; o < p.ws; ++o) ptx::red_relaxed_sys_add(p.flags[(me + o) % p.ws] + g, 1u);
+            if constexpr (TRACE) stamp(s_sig_t[slot], kTraceSignalled);
+            ptx::mbar_arrive(&sig_empty_bar[slot]);
+          }
+          n += m;
         }
       }
     }
