@@ -69,7 +69,7 @@ namespace fo {
 
 // Tiles that the push warp may have handed to the signal warp without their arrival having been
 // announced yet (fused kernels).
-constexpr int kSigRing = 4;
+constexpr int kSigRing = 8;
 
 template <int BN, int STAGES, bool CTA2 = false, int MT = 1, int EPI = 2>
 struct GemmSmem {
@@ -85,7 +85,7 @@ struct GemmSmem {
   // + chunk_ready[EPI], chunk_free[EPI], sig_full[kSigRing], sig_empty[kSigRing]
   static constexpr int kNumBars = 2 * STAGES + 4 + 2 * EPI + 2 * kSigRing;
   static constexpr int kMiscOffset = kBarOffset + kNumBars * 8;
-  static constexpr int kMiscBytes = 64;
+  static constexpr int kMiscBytes = 128;
   // +1024: the ring is aligned up to 1024 B at run time (128-byte swizzle atom).
   static constexpr int kTotalBytes = kMiscOffset + kMiscBytes + 1024;
 };
@@ -471,7 +471,7 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
   volatile int* s_red_ok = reinterpret_cast<volatile int*>(misc + 4);
   // ring between the push warp and the signal warp: wave group and tile id of each handed-over tile
   volatile int* s_sig_g = reinterpret_cast<volatile int*>(misc + 8);
-  volatile int* s_sig_t = reinterpret_cast<volatile int*>(misc + 12);
+  volatile int* s_sig_t = reinterpret_cast<volatile int*>(misc + 8 + kSigRing);
 
   const int warp_idx = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;

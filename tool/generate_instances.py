@@ -33,14 +33,15 @@ PY = os.path.join(ROOT, "flashoverlap_b200", "utils", "_instances.py")
 BM, BK = 128, 64
 SMEM_LIMIT = 227 * 1024
 TMEM_COLS = 512
+SIG_RING = 8   # slots of the ring between the push warp and the signal warp (kSigRing)
 
 
 def smem_bytes(bn: int, stages: int, cta2: int, mt: int, epi: int = 2) -> int:
     """Dynamic shared memory of one instantiation (mirrors GemmSmem in fo_gemm_sm100.cuh)."""
     a = mt * BM * BK * 2
     b = (bn // 2 if cta2 else bn) * BK * 2
-    bars = (2 * stages + 4 + 2 * epi) * 8
-    return stages * (a + b) + epi * BM * 128 + bars + 64 + 1024
+    bars = (2 * stages + 4 + 2 * epi + 2 * SIG_RING) * 8
+    return stages * (a + b) + epi * BM * 128 + bars + 128 + 1024
 
 
 def check_kernel(k: dict) -> None:
