@@ -269,3 +269,55 @@ def test_all2all_handshakes_under_random_interleavings(seed):
     else:
         raise AssertionError("the handshake got stuck")
     assert reads == ws * calls
+
+
+@pytest.mark.parametrize("ring", [1, 4, 8])
+@pytest.mark.parametrize("seed", [0, 1, 2, 3])
+def test_signal_ring_between_push_and_signal_warp(ring, seed):
+    """The ring through which the push warp hands finished tiles to the signal warp of the fused
+    kernels (csrc/gemm/fo_gemm_sm100.cuh: sig_full / sig_empty mbarriers, slot = count % ring,
+    parities from the running counts; the signal warp takes every slot that is already full and
+    publishes the batch behind ONE fence).  Under random interleavings: a slot is never rewritten
+    before the signal warp has read it, every tile is published exactly once and in order, a tile
+    is never published before its stores completed, and both sides terminate."""
+    rng = random.Random(100 * ring + seed)
+    n_tiles = 41
+    full = [_Mbar(1) for _ in range(ring)]
+    empty = [_Mbar(1) for _ in range(ring)]
+    slot_tile = [None] * ring
+    slot_unread = [False] * ring
+    stores_done = set()
+    published = []
+    fences = 0
+    handed, taken = 0, 0
+    steps = 0
+    while taken < n_tiles and steps < 200000:
+        steps += 1
+        if rng.random() < 0.5:
+            if handed < n_tiles:
+                s = handed % ring
+                if not empty[s].passed(((handed // ring) & 1) ^ 1):
+                    continue                      # ring full: the push warp waits (bounded in the kernel)
+                stores_done.add(handed)           # cp.async.bulk.wait_group: the tile's stores have landed
+                assert not slot_unread[s], f"slot {s} rewritten before tile {slot_tile[s]} was read"
+                slot_tile[s], slot_unread[s] = handed, True
+                full[s].arrive()
+                handed += 1
+        else:
+            s = taken % ring
+            if not full[s].passed((taken // ring) & 1):
+                continue
+            m = 1
+            while taken + m < n_tiles and m < ring and full[(taken + m) % ring].passed(((taken + m) // ring) & 1):
+                m += 1
+            fences += 1                           # one system-scope release fence for the whole batch
+            for j in range(m):
+                sj = (taken + j) % ring
+                t = slot_tile[sj]
+                assert t == taken + j and t in stores_done
+                published.append(t)
+                slot_unread[sj] = False
+                empty[sj].arrive()
+            taken += m
+    assert published == list(range(n_tiles))
+    assert fences <= n_tiles and (ring == 1 or fences >= 1)
