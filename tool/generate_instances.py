@@ -46,8 +46,8 @@ def smem_bytes(bn: int, stages: int, cta2: int, mt: int, epi: int = 2) -> int:
 
 def check_kernel(k: dict) -> None:
     bn, st, c2, mt = k["bn"], k["stages"], k["cta2"], k["mt"]
-    if bn not in (64, 128, 192, 256) or bn % 64:
-        raise ValueError(f"bn={bn}: the tile width must be a multiple of 64 up to 256")
+    if bn not in (128, 256):
+        raise ValueError(f"bn={bn}: the kernel template is written for tile widths of 128 and 256 columns")
     if mt not in (1, 2) or (mt == 2 and not (c2 and bn == 256)):
         raise ValueError("mt=2 (two 128-row halves per CTA) needs cta2=1 and bn=256")
     if c2 not in (0, 1):
