@@ -88,7 +88,7 @@ def worker(rank, world, args):
 
                         def measure_fused(cseg):
                             wl.set_cseg(cseg)
-                            return perf_ms(wl.run, 3, max(5, args.reps // 2), args.flush)
+                            return perf_ms(wl.run, args.warmup, args.reps, args.flush)
 
                         cs_e, t_e, _ = tuner.exhaustive_search(f_cands, measure_fused)
                         rec.update(fused_best_groups=len(cs_e), fused_best_ms=round(t_e, 5))
