@@ -11,6 +11,7 @@ output and prints the time of each.  Random-init bf16 weights ~N(0, 0.02); hidde
 """
 import argparse
 import json
+import time
 
 import _common  # noqa: F401
 import torch
@@ -47,7 +48,17 @@ def worker(rank, world, args):
         x_sp = x_full[rows].contiguous()
         with torch.no_grad():
             y = layer(x_sp)
-            res[name] = perf_ms(lambda: layer(x_sp), args.warmup, args.reps)
+            # every arm settles under about a second of its own load first: the board runs at its
+            # power cap, and an arm timed right after another one's cool start reads faster
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            layer(x_sp)
+            torch.cuda.synchronize()
+            one = torch.tensor([max(time.perf_counter() - t0, 1e-4)], device="cuda")
+            if world > 1:
+                dist.all_reduce(one, op=dist.ReduceOp.MAX)
+            settle = int(min(200, args.settle_s / one.item()))
+            res[name] = perf_ms(lambda: layer(x_sp), max(args.warmup, settle), args.reps)
             if not tail:
                 # the two row-parallel projections alone (GEMM + reduce-scatter), same operand shapes
                 attn = torch.randn(T, layer.q_local * cfg.head_dim, device="cuda").to(torch.bfloat16) * 0.1
@@ -86,6 +97,7 @@ def main():
     ap.add_argument("--pull", action="store_true", help="fused kernels use the pull protocol (in-switch reduction)")
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--reps", type=int, default=10)
+    ap.add_argument("--settle_s", type=float, default=1.0, help="seconds of load before each arm is timed")
     args = ap.parse_args()
     ok = run_on_all_gpus(worker, args)
     raise SystemExit(0 if ok else 1)
