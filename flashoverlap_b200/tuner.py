@@ -28,6 +28,9 @@ import torch
 from .utils import layout
 
 BANDWIDTH_POINTS = 36
+# Fused-mode model constants (see predict_latency)
+kFusedComputeFactor = 1.05
+kFusedTailMs = 0.030
 
 
 def bandwidth_sizes() -> List[int]:
@@ -111,9 +114,24 @@ def predict_latency(p: Problem, cseg: Sequence[int], curve: torch.Tensor, mode: 
         comp_of = lambda tiles: per_wave * layout.div_up(tiles, wave)
         del new_waves
     elif mode == "fused":
-        # tiles retire continuously on a persistent grid: compute time is proportional to tiles
-        per_tile = p.gemm_ms / layout.div_up(p.tiles, full_grid) / full_grid
+        # Tiles retire continuously on a persistent grid: compute time is proportional to tiles.
+        # Fitted on the tp2 / tp8 sweeps (profiles/sweep_tp*.md): the fused kernel's main loop runs
+        # about 5 % slower than the plain GEMM's (its epilogue feeds the push warp), the groups'
+        # transfers stream back to back at the curve's ASYMPTOTIC bandwidth (a group's message is
+        # not a collective call of its own: the per-call latency that the small-message end of the
+        # curve contains is paid once, as the tail after the last group), and that tail - pipeline fill,
+        # the last tile's reduction and the end-of-call handshake - is about 30 us.  Mean |error| of
+        # the fit on the tp2 sweep: 6 %, worst 16 % (the 1024-row shapes).
+        per_tile = kFusedComputeFactor * p.gemm_ms / layout.div_up(p.tiles, full_grid) / full_grid
         comp_of = lambda tiles: per_tile * tiles
+        bw_inf = float(curve[:, 1].max())
+        comm = lambda tiles: algorithmic_bytes(tiles * p.tile_elems, p.comm_op, p.world_size) / bw_inf / 2 ** 30
+        comp_t, comm_t = 0.0, 0.0
+        for i, g in enumerate(cseg):
+            prev_comm = comm(cseg[i - 1]) if i > 0 else 0.0
+            comm_t = max(comp_t, comm_t) + prev_comm
+            comp_t += comp_of(g)
+        return max(comp_t, comm_t) + comm(cseg[-1]) + kFusedTailMs
     else:
         raise ValueError("mode must be 'gated' or 'fused'")
     comp_t, comm_t = 0.0, 0.0
