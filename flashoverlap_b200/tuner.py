@@ -31,6 +31,7 @@ BANDWIDTH_POINTS = 36
 # Fused-mode model constants (see predict_latency)
 kFusedComputeFactor = 1.05
 kFusedTailMs = 0.030
+kGatedCommFactor = 1.2
 
 
 def bandwidth_sizes() -> List[int]:
@@ -107,6 +108,10 @@ def predict_latency(p: Problem, cseg: Sequence[int], curve: torch.Tensor, mode: 
         return p.gemm_ms + comm(cseg[0])
     full_grid = p.grid or p.sm_count
     if mode == "gated":
+        # A collective that runs under the GEMM shares SMs, L2 and power with it: fitted on the
+        # tp2 / tp4 sweeps, it takes about 1.2x its stand-alone time from the curve.
+        base_comm = comm
+        comm = lambda tiles: kGatedCommFactor * base_comm(tiles)
         wave = max(1, p.sm_count - p.sm_margin)
         old_waves = layout.div_up(p.tiles, p.sm_count)
         new_waves = layout.div_up(p.tiles, wave)

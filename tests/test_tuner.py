@@ -35,7 +35,9 @@ def test_predict_latency_gated_matches_hand_computation():
     per_tile = tuner.comm_latency_ms(curve, p.tile_elems, "all_reduce", 2)
     # one group: no overlap
     assert tuner.predict_latency(p, [584], curve, "gated") == pytest.approx(4.0 + 584 * per_tile)
-    # two groups of two waves: comm of group 0 hides under compute of group 1
+    # two groups of two waves: comm of group 0 hides under compute of group 1; a collective that
+    # runs beside the GEMM is charged kGatedCommFactor times its stand-alone time
+    per_tile *= tuner.kGatedCommFactor
     c = 292 * per_tile
     expect = max(4.0, 2.0 + c) + c
     assert tuner.predict_latency(p, [292, 292], curve, "gated") == pytest.approx(expect)
