@@ -431,3 +431,59 @@ def test_rejected_call_keeps_ranks_in_step(lib):
     world = _world()
     for r in run_ranks(_rejected_call_worker, world, "nccl"):
         assert r["raised"] and r["status"] == 0 and r["err"] <= 1.0, r
+
+
+def _launch_skew_worker(rank, world):
+    """Back-to-back fused calls with no barrier between them while, at every call, another rank
+    reaches its launch tens of milliseconds late: the call-number handshake in the kernels must
+    keep a fast rank's next call from overwriting staging or results a slow rank still needs.
+    Operands change from call to call (exact power-of-two scales), so a stale slice would show."""
+    import time
+    from flashoverlap_b200.parallel import symm
+    from flashoverlap_b200.utils import config, layout
+    dev = torch.device("cuda", rank)
+    impl = _setup(rank, world)
+    M, N, K, algo = 2048, 2048, 512, 1
+    BM = config.algo_params(algo)["BM"]
+    A, B = _rand((M, K), dev, 50 + rank), _rand((N, K), dev, 60 + rank)
+    ref = A.float() @ B.float().t()
+    dist.all_reduce(ref)
+    tol = 0.02 * ref.abs().max().item() + 1e-3
+    rows = layout.owned_rows(M, BM, world, rank, True).to(dev)
+    scales = (1.0, 4.0, 0.5, 2.0, 0.25, 8.0, 1.0, 2.0)
+    res = {}
+    for protocol in ("push", "pull"):
+        impl.set_option("stage_local", 1 if protocol == "pull" else 0)
+        C, _ = symm.alloc_allreduce_output(impl, (M, N), torch.bfloat16)
+        D = torch.empty(M // world, N, device=dev, dtype=torch.bfloat16)
+        torch.cuda.synchronize(); dist.barrier()
+        snaps = []
+        for i, s in enumerate(scales):
+            if i % world == rank:
+                time.sleep(0.03)                      # this rank launches late
+            elif (i + 1) % world == rank:
+                torch.cuda._sleep(20_000_000)         # this one is late on the device (~10 ms)
+            As = A * s
+            if i % 2 == 0:
+                impl.gemm_allreduce_fused(As, B, C, algo)
+                snaps.append((s, None, C.clone()))    # stream-ordered before this rank's next call
+            else:
+                D.fill_(float("nan"))
+                impl.gemm_reducescatter_fused(As, B, D, algo)
+                snaps.append((s, rows, D.clone()))
+        torch.cuda.synchronize(); dist.barrier()
+        worst = 0.0
+        for s, r, got in snaps:
+            want = ref * s if r is None else ref[r] * s
+            worst = max(worst, (got.float() - want).abs().max().item() / (tol * s))
+        res[f"skew_{protocol}"] = worst
+    res["status"] = impl.read_status()[0]
+    return res
+
+
+def test_launch_skew_between_ranks(lib):
+    world = _world()
+    for r in run_ranks(_launch_skew_worker, world, "nccl"):
+        assert r.pop("status") == 0
+        for k, v in r.items():
+            assert v <= 1.0, (k, v)
