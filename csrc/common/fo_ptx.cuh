@@ -96,6 +96,20 @@ FO_DEVICE bool mbar_try_wait_suspend(uint64_t* bar, uint32_t parity, uint32_t su
   return ok != 0;
 }
 
+// One lane of the (converged) warp, chosen by the hardware: true in that lane only.  Roles whose
+// loops every lane walks use it to predicate the single-thread instructions (TMA, MMA, commits).
+FO_DEVICE bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "elect.sync _|p, 0xffffffff;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(pred));
+  return pred != 0;
+}
+
 // Time base of the bounded waits: the SM cycle counter.  Reading %globaltimer costs on the
 // order of a microsecond, which is ruinous inside a hand-off between warps that happens several
 // times per tile; clock64 costs a few cycles.  Timeouts given in nanoseconds are converted

@@ -473,7 +473,9 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
   volatile int* s_sig_g = reinterpret_cast<volatile int*>(misc + 8);
   volatile int* s_sig_t = reinterpret_cast<volatile int*>(misc + 8 + kSigRing);
 
-  const int warp_idx = threadIdx.x >> 5;
+  // broadcast from lane 0 so that the compiler knows the role index is the same in every lane and
+  // can keep the role loops' counters and addresses in uniform registers
+  const int warp_idx = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);
   const int lane = threadIdx.x & 31;
   const int vr = blockIdx.y;           // virtual rank of this CTA inside the launch
   const int me = p.rank_base + vr;     // rank this CTA acts as
@@ -548,7 +550,10 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
 
   if (warp_idx == 0) {
     // ------------------------------------------------------------------ TMA producer
-    if (lane == 0) {
+    // The whole warp walks the loops (so their control flow is warp-uniform) and one elected
+    // lane issues the copies.
+    {
+      const bool elected = ptx::elect_one();
       int stage = 0;
       uint32_t phase = 0;
       uint32_t issued = 0;
@@ -557,28 +562,31 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
         const TileCoord tc = my_tile(pos);
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!ptx::mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, s_abort, pipe_timeout, p.wait_sleep_ns)) {
-            ptx::report_status(status, kStatusTimeoutSmemEmpty, pos, kb, stage);
+            if (elected) ptx::report_status(status, kStatusTimeoutSmemEmpty, pos, kb, stage);
             *s_abort = 1;
             ok = false;
             break;
           }
           uint8_t* sa = smem + stage * L::kStageBytes;
           uint8_t* sb = sa + L::kABytes;
-          if constexpr (CTA2) {
-            // The leader's barrier collects the bytes of both CTAs.
-            if (leader) ptx::mbar_arrive_expect_tx(&full_bar[stage], 2 * L::kStageBytes);
+          if (elected) {
+            if constexpr (CTA2) {
+              // The leader's barrier collects the bytes of both CTAs.
+              if (leader) ptx::mbar_arrive_expect_tx(&full_bar[stage], 2 * L::kStageBytes);
 #pragma unroll
-            for (int h = 0; h < MT; ++h) {
-              ptx::tma_load_2d_pair(sa + h * L::kAHalfBytes, &maps.a[vr], &full_bar[stage], kb * kBK,
-                                    (tc.m + h) * kBM, p.l2_hint_a);
+              for (int h = 0; h < MT; ++h) {
+                ptx::tma_load_2d_pair(sa + h * L::kAHalfBytes, &maps.a[vr], &full_bar[stage], kb * kBK,
+                                      (tc.m + h) * kBM, p.l2_hint_a);
+              }
+              ptx::tma_load_2d_pair(sb, &maps.b[vr], &full_bar[stage], kb * kBK,
+                                    tc.n * BN + static_cast<int>(cta_rank) * L::kBRows, p.l2_hint_b);
+            } else {
+              ptx::mbar_arrive_expect_tx(&full_bar[stage], L::kStageBytes);
+              ptx::tma_load_2d(sa, &maps.a[vr], &full_bar[stage], kb * kBK, tc.m * kBM, p.l2_hint_a);
+              ptx::tma_load_2d(sb, &maps.b[vr], &full_bar[stage], kb * kBK, tc.n * BN, p.l2_hint_b);
             }
-            ptx::tma_load_2d_pair(sb, &maps.b[vr], &full_bar[stage], kb * kBK,
-                                  tc.n * BN + static_cast<int>(cta_rank) * L::kBRows, p.l2_hint_b);
-          } else {
-            ptx::mbar_arrive_expect_tx(&full_bar[stage], L::kStageBytes);
-            ptx::tma_load_2d(sa, &maps.a[vr], &full_bar[stage], kb * kBK, tc.m * kBM, p.l2_hint_a);
-            ptx::tma_load_2d(sb, &maps.b[vr], &full_bar[stage], kb * kBK, tc.n * BN, p.l2_hint_b);
           }
+          __syncwarp();
           ++issued;
           if (++stage == STAGES) {
             stage = 0;
@@ -591,7 +599,7 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
       // (In a pair the follower's loads are counted on the leader's barriers, which the
       // follower cannot poll; it relies on the cluster-wide barrier at the end instead: the
       // leader reaches it only after draining the barriers that count both CTAs' bytes.)
-      for (int s = 0; s < STAGES && (!CTA2 || leader); ++s) {
+      for (int s = 0; elected && s < STAGES && (!CTA2 || leader); ++s) {
         if (issued <= static_cast<uint32_t>(s)) continue;
         const uint32_t last = ((issued - 1 - s) / STAGES) * STAGES + s;  // last issue index on slot s
         const uint32_t par = (last / STAGES) & 1u;
@@ -602,7 +610,9 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
     }
   } else if (warp_idx == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0 && leader) {
+    // The leader's whole warp walks the loops; one elected lane issues the MMAs and commits.
+    if (leader) {
+      const bool elected = ptx::elect_one();
       constexpr uint32_t idesc = ptx::make_idesc_f16(BF16, CTA2 ? 2 * kBM : kBM, BN);
       int stage = 0;
       uint32_t phase = 0;
@@ -611,7 +621,7 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
       bool ok = true;
       for (int pos = unit; ok && pos < sched_tiles; pos += num_units) {
         if (!ptx::mbar_wait_bounded(&tmem_empty_bar[acc], acc_phase ^ 1u, s_abort, pipe_timeout, p.wait_sleep_ns)) {
-          ptx::report_status(status, kStatusTimeoutTmemEmpty, pos, acc, 0);
+          if (elected) ptx::report_status(status, kStatusTimeoutTmemEmpty, pos, acc, 0);
           *s_abort = 1;
           break;
         }
@@ -619,7 +629,7 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
         const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(acc * BN);
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!ptx::mbar_wait_bounded(&full_bar[stage], phase, s_abort, pipe_timeout, p.wait_sleep_ns)) {
-            ptx::report_status(status, kStatusTimeoutSmemFull, pos, kb, stage);
+            if (elected) ptx::report_status(status, kStatusTimeoutSmemFull, pos, kb, stage);
             *s_abort = 1;
             ok = false;
             break;
@@ -628,47 +638,53 @@ __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsPlain, 1)
           const uint32_t sa = ptx::smem_u32(smem + stage * L::kStageBytes);
           const uint64_t da = ptx::make_smem_desc_sw128_kmajor(sa);
           const uint64_t db = ptx::make_smem_desc_sw128_kmajor(sa + L::kABytes);
-          // advance 16 elements (32 B) along K inside the swizzle atom: +2 in 16-byte units
-          if constexpr (CTA2) {
+          if (elected) {
+            // advance 16 elements (32 B) along K inside the swizzle atom: +2 in 16-byte units
+            if constexpr (CTA2) {
 #pragma unroll
-            for (int h = 0; h < MT; ++h) {
-              // half h: its A rows sit h * 16 KB further in the stage, its accumulator BN
-              // columns further in TMEM; both halves multiply the same B tile.  The four MMAs
-              // of a half are issued back to back so that consecutive instructions accumulate
-              // into the same TMEM columns.
+              for (int h = 0; h < MT; ++h) {
+                // half h: its A rows sit h * 16 KB further in the stage, its accumulator BN
+                // columns further in TMEM; both halves multiply the same B tile.  The four MMAs
+                // of a half are issued back to back so that consecutive instructions accumulate
+                // into the same TMEM columns.
+#pragma unroll
+                for (int k = 0; k < kBK / 16; ++k) {
+                  ptx::umma_f16_ss_pair(tmem_d + static_cast<uint32_t>(h * BN),
+                                        da + static_cast<uint64_t>(h * (L::kAHalfBytes >> 4) + 2 * k),
+                                        db + static_cast<uint64_t>(2 * k), idesc,
+                                        (kb > 0 || k > 0) ? 1u : 0u);
+                }
+              }
+            } else {
 #pragma unroll
               for (int k = 0; k < kBK / 16; ++k) {
-                ptx::umma_f16_ss_pair(tmem_d + static_cast<uint32_t>(h * BN),
-                                      da + static_cast<uint64_t>(h * (L::kAHalfBytes >> 4) + 2 * k),
-                                      db + static_cast<uint64_t>(2 * k), idesc,
-                                      (kb > 0 || k > 0) ? 1u : 0u);
+                ptx::umma_f16_ss(tmem_d, da + static_cast<uint64_t>(2 * k),
+                                 db + static_cast<uint64_t>(2 * k), idesc,
+                                 (kb > 0 || k > 0) ? 1u : 0u);
               }
             }
-          } else {
-#pragma unroll
-            for (int k = 0; k < kBK / 16; ++k) {
-              ptx::umma_f16_ss(tmem_d, da + static_cast<uint64_t>(2 * k),
-                               db + static_cast<uint64_t>(2 * k), idesc,
-                               (kb > 0 || k > 0) ? 1u : 0u);
+            // slot reusable (in both CTAs of a pair) once these MMAs have read it
+            if constexpr (CTA2) {
+              ptx::umma_commit_pair(&empty_bar[stage], 3);
+            } else {
+              ptx::umma_commit(&empty_bar[stage]);
             }
           }
-          // slot reusable (in both CTAs of a pair) once these MMAs have read it
-          if constexpr (CTA2) {
-            ptx::umma_commit_pair(&empty_bar[stage], 3);
-          } else {
-            ptx::umma_commit(&empty_bar[stage]);
-          }
+          __syncwarp();
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1u;
           }
         }
         if (!ok) break;
-        if constexpr (CTA2) {
-          ptx::umma_commit_pair(&tmem_full_bar[acc], 3);  // accumulators complete in both CTAs
-        } else {
-          ptx::umma_commit(&tmem_full_bar[acc]);
+        if (elected) {
+          if constexpr (CTA2) {
+            ptx::umma_commit_pair(&tmem_full_bar[acc], 3);  // accumulators complete in both CTAs
+          } else {
+            ptx::umma_commit(&tmem_full_bar[acc]);
+          }
         }
+        __syncwarp();
         if (++acc == kAccStages) {
           acc = 0;
           acc_phase ^= 1u;

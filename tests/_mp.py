@@ -56,15 +56,24 @@ def _entry(rank, world, backend, port, fn, args, result_dir, timeout_s):
 
 
 def run_ranks(fn, world: int, backend: str = "gloo", args=(), timeout_s: int = 60):
-    """Runs fn(rank, world, *args) in `world` processes; returns the per-rank results."""
-    with tempfile.TemporaryDirectory() as d:
-        try:
-            mp.spawn(_entry, args=(world, backend, free_port(), fn, args, d, timeout_s), nprocs=world, join=True)
-        except Exception as ex:
-            errs = []
-            for r in range(world):
-                p = os.path.join(d, f"r{r}.err")
-                if os.path.exists(p):
-                    errs.append(f"--- rank {r} ---\n" + open(p).read())
-            raise AssertionError("rank failure:\n" + "\n".join(errs) + f"\n{ex}") from ex
-        return [torch.load(os.path.join(d, f"r{r}.pt"), weights_only=False) for r in range(world)]
+    """Runs fn(rank, world, *args) in `world` processes; returns the per-rank results.
+
+    The rendezvous port is picked by binding to port 0 and closing the socket, so another process
+    (or a lingering socket of the previous test) can take it before rank 0 listens on it; a run
+    that fails with "address already in use" is repeated on a fresh port, twice at most."""
+    for attempt in range(3):
+        with tempfile.TemporaryDirectory() as d:
+            try:
+                mp.spawn(_entry, args=(world, backend, free_port(), fn, args, d, timeout_s), nprocs=world, join=True)
+            except Exception as ex:
+                errs = []
+                for r in range(world):
+                    p = os.path.join(d, f"r{r}.err")
+                    if os.path.exists(p):
+                        errs.append(f"--- rank {r} ---\n" + open(p).read())
+                text = "\n".join(errs) + f"\n{ex}"
+                if attempt < 2 and ("EADDRINUSE" in text or "address already in use" in text):
+                    time.sleep(1.0)
+                    continue
+                raise AssertionError("rank failure:\n" + text) from ex
+            return [torch.load(os.path.join(d, f"r{r}.pt"), weights_only=False) for r in range(world)]
