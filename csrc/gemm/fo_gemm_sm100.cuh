@@ -18,6 +18,9 @@
 //   warp 1      MMA issuer: one thread issues tcgen05.mma.kind::f16 (fp32 accumulate in TMEM),
 //               tcgen05.commit releases ring slots and publishes finished accumulators;
 //               this warp also owns the TMEM allocation (2 accumulators of BN columns);
+//               (warps 0 and 1 walk their loops with all lanes, waits included, and a lane
+//               chosen by elect.sync issues: warp-uniform control flow lets the compiler keep
+//               counters, addresses and descriptors in uniform registers)
 //   warps 2-5   epilogue: tcgen05.ld -> convert -> swizzled shared-memory transpose ->
 //               128-byte coalesced global (local or peer) stores, then the signal;
 //   warps 6-9   (fused only) reducer for the row slices this rank owns;
