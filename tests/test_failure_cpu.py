@@ -81,3 +81,32 @@ def test_status_words_become_exception(lib):
     assert "unknown" in msg([77, 0, 0, 0, 0, 0, 0, 0], 0)
     with pytest.raises(RuntimeError, match="status block"):
         msg([1, 2], 0)
+
+
+def test_rank_runner_retries_on_a_taken_rendezvous_port(monkeypatch):
+    """The helper that runs test ranks picks its port by bind-and-close, so the port can be
+    taken before rank 0 listens on it; such a run is repeated on a fresh port, other failures
+    are not."""
+    from tests import _mp
+    real_spawn = _mp.mp.spawn
+    calls = {"n": 0}
+
+    def flaky_spawn(*a, **kw):
+        calls["n"] += 1
+        if calls["n"] == 1:
+            raise RuntimeError("The server socket has failed to listen ... EADDRINUSE, address already in use")
+        return real_spawn(*a, **kw)
+
+    monkeypatch.setattr(_mp.mp, "spawn", flaky_spawn)
+    monkeypatch.setattr(_mp.time, "sleep", lambda s: None)
+    assert _mp.run_ranks(_healthy, 2, "gloo") == [3.0, 3.0]
+    assert calls["n"] == 2
+
+    def broken_spawn(*a, **kw):
+        calls["n"] += 1
+        raise RuntimeError("something else")
+
+    monkeypatch.setattr(_mp.mp, "spawn", broken_spawn)
+    with pytest.raises(AssertionError, match="something else"):
+        _mp.run_ranks(_healthy, 2, "gloo")
+    assert calls["n"] == 3
