@@ -12,7 +12,10 @@ Two implementations of the same math:
   * ``impl="fused"``: one sm_100a kernel per projection that computes the tiles and
     reduce-scatters them over NVLink as they retire.  With the fused kernel every 128-token tile
     is split across the ranks (rank r owns tokens ``r*128/tp .. (r+1)*128/tp - 1`` of each
-    tile), so the all-gather that follows restores token order with one strided copy.
+    tile), so an all-gather delivers the tokens tile-interleaved.  The gathered activations are
+    NOT re-ordered: the column-parallel GEMMs do not care about row order, the (much narrower)
+    QKV result is put into token order by the copy that splits it into heads, and SwiGLU writes
+    its product straight into token order (``layout.tokens_as_gathered`` as the ``out=`` view).
 """
 from __future__ import annotations
 
@@ -122,11 +125,13 @@ class TPDecoderLayer(nn.Module):
         n, h = x_sp.shape
         buf = torch.empty((self.world, n, h), dtype=x_sp.dtype, device=x_sp.device)
         dist.all_gather_into_tensor(buf, x_sp.contiguous(), group=self.group)
-        if self.impl == "fused":
-            ro = TILE_M // self.world
-            # [rank, tile, row in block, h] -> [tile, rank, row in block, h]
-            return buf.view(self.world, n // ro, ro, h).permute(1, 0, 2, 3).reshape(self.world * n, h)
+        # impl="fused": rows in gather order (rank-major), see _gathered
         return buf.view(self.world * n, h)
+
+    @property
+    def _gathered(self) -> bool:
+        """True when all-gathered activations are tile-interleaved (fused ownership)."""
+        return self.impl == "fused" and self.world > 1
 
     def _row_parallel(self, x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
         """[T, k_local] @ weight[h, k_local]^T, summed over ranks, scattered over tokens."""
@@ -147,6 +152,9 @@ class TPDecoderLayer(nn.Module):
         # attention block
         xn = self._all_gather_tokens(self._norm(x_sp, self.attn_norm))          # [T, h]
         qkv = torch.matmul(xn, self.wqkv.t())
+        if self._gathered:
+            # token order for attention; this matrix is (q_local + 2 kv_local) * hd wide, not h
+            qkv = layout.gathered_as_tokens(qkv, self.world, TILE_M).reshape(B * S, -1)
         q, k, v = qkv.split([self.q_local * hd, self.kv_local * hd, self.kv_local * hd], dim=-1)
         q = q.view(B, S, self.q_local, hd).transpose(1, 2)
         k = k.view(B, S, self.kv_local, hd).transpose(1, 2)
@@ -167,5 +175,15 @@ class TPDecoderLayer(nn.Module):
         # MLP block
         gu = torch.matmul(hn, self.wgu.t())
         gate, up = gu.split([self.ffn_local, self.ffn_local], dim=-1)
-        act = F.silu(gate) * up
+        if self._gathered and not (torch.is_grad_enabled() and gu.requires_grad):
+            # gate and up are in gather order; the product lands in token order, where the
+            # row-parallel projection (and its token ownership) needs it
+            act = torch.empty((B * S, self.ffn_local), dtype=gu.dtype, device=gu.device)
+            dst = layout.tokens_as_gathered(act, self.world, TILE_M)
+            torch.mul(F.silu(gate).view(dst.shape), up.view(dst.shape), out=dst)
+        elif self._gathered:
+            # out= is closed to autograd: the same placement as a copy of its own
+            act = layout.gathered_as_tokens(F.silu(gate) * up, self.world, TILE_M).reshape(B * S, self.ffn_local)
+        else:
+            act = F.silu(gate) * up
         return h_sp + self._row_parallel(act, self.wd)

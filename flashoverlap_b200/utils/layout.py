@@ -125,6 +125,31 @@ def owned_rows(M: int, BM: int, world_size: int, rank: int, strided: bool = True
     return idx[(idx % BM) // (BM // world_size) == rank]
 
 
+def gathered_as_tokens(buf: torch.Tensor, world_size: int, BM: int = 128) -> torch.Tensor:
+    """Token-ordered VIEW of an all-gathered matrix whose shards follow the contiguous-block
+    ownership of the fused reduce-scatter (``owned_rows(..., strided=False)``).
+
+    ``buf`` is ``[world_size * n, c]`` in gather order (rank-major).  Rank r's shard holds rows
+    ``r*BM/ws .. (r+1)*BM/ws - 1`` of every BM-row tile, so token ``tile*BM + r*BM/ws + i`` sits at
+    ``buf[r*n + tile*BM/ws + i]``.  The result has shape ``[tiles, world_size, BM/ws, c]`` and is
+    not contiguous: ``.reshape(-1, c)`` copies it into token order, and as the ``out=`` of an
+    elementwise op over rank-major inputs it places their result in token order without a pass
+    of its own (give it a token-ordered buffer and use the result of
+    ``gathered_as_tokens(buffer.view_as(rank_major), ...)`` the other way round, see
+    ``tokens_as_gathered``)."""
+    rows, c = buf.shape
+    n, ro = rows // world_size, BM // world_size
+    return buf.view(world_size, n // ro, ro, c).permute(1, 0, 2, 3)
+
+
+def tokens_as_gathered(buf: torch.Tensor, world_size: int, BM: int = 128) -> torch.Tensor:
+    """The inverse view: a token-ordered ``[T, c]`` matrix indexed ``[rank, tile, row in block, c]``,
+    i.e. in the order an all-gather of the ranks' shards delivers."""
+    rows, c = buf.shape
+    ro = BM // world_size
+    return buf.view(rows // BM, world_size, ro, c).permute(1, 0, 2, 3)
+
+
 # ----------------------------------------------------------------------------- layouts
 
 def _tile_offsets(M, N, BM, BN, RA, rldn):

@@ -110,3 +110,24 @@ def test_rmsnorm_ref_matches_manual():
     y = layout.rmsnorm_ref(x, w, 1e-6)
     manual = x / torch.sqrt((x * x).mean(-1, keepdim=True) + 1e-6) * w
     assert torch.allclose(y, manual, atol=1e-6)
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_gathered_views_restore_token_order(world):
+    """Shards cut by the contiguous-block ownership, concatenated in rank order (what an
+    all-gather delivers), read through gathered_as_tokens are the tokens in order; an
+    elementwise op over rank-major inputs with tokens_as_gathered(out) as its destination
+    lands in token order."""
+    T, c, BM = 512, 24, 128
+    tokens = torch.arange(T * c, dtype=torch.float32).reshape(T, c)
+    shards = [tokens[layout.owned_rows(T, BM, world, r, strided=False)] for r in range(world)]
+    gathered = torch.cat(shards)
+    assert torch.equal(layout.gathered_as_tokens(gathered, world, BM).reshape(T, c), tokens)
+    # column slices of a wider rank-major matrix, as the gate / up halves of an MLP are
+    wide = torch.cat([gathered, 2 * gathered], dim=1)
+    a, b = wide.split([c, c], dim=1)
+    n, ro = T // world, BM // world
+    out = torch.full((T, c), float("nan"))
+    torch.mul(a.reshape(world, n // ro, ro, c), b.view(world, n // ro, ro, c),
+              out=layout.tokens_as_gathered(out, world, BM))
+    assert torch.equal(out, 2 * tokens * tokens)
