@@ -81,7 +81,7 @@ class TPDecoderLayer(nn.Module):
         # impl="fused" only: o_proj's residual add and the RMSNorm that follows it run inside the
         # reduce-scatter kernel's reducers (gemm_reducescatter_add_rmsnorm_fused)
         self.fuse_norm = bool(fuse_norm) and impl == "fused" and world > 1
-        if impl == "fused" and world > 1:
+        if impl == "fused" and world > 1 and torch.device(device).type == "cuda":
             assert overlap_impl is not None, "impl='fused' needs an OverlapImpl"
             overlap_impl.set_option("strided_rows", 0)  # contiguous blocks inside each tile
         h, hd = cfg.hidden, cfg.head_dim
@@ -123,10 +123,9 @@ class TPDecoderLayer(nn.Module):
         if self.world == 1:
             return x_sp
         n, h = x_sp.shape
-        buf = torch.empty((self.world, n, h), dtype=x_sp.dtype, device=x_sp.device)
+        buf = torch.empty((self.world * n, h), dtype=x_sp.dtype, device=x_sp.device)
         dist.all_gather_into_tensor(buf, x_sp.contiguous(), group=self.group)
-        # impl="fused": rows in gather order (rank-major), see _gathered
-        return buf.view(self.world * n, h)
+        return buf           # impl="fused": rows in gather order (rank-major), see _gathered
 
     @property
     def _gathered(self) -> bool:
@@ -138,6 +137,12 @@ class TPDecoderLayer(nn.Module):
         T = x.shape[0]
         if self.world == 1:
             return torch.matmul(x, weight.t())
+        if not x.is_cuda:
+            # CPU ranks (tests of the layer's data flow): the same sums and the same token
+            # ownership as the kernels, by an all-reduce and a row selection
+            full = torch.matmul(x, weight.t())
+            dist.all_reduce(full, group=self.group)
+            return full[self.shard_rows()]
         out = torch.empty((T // self.world, weight.shape[0]), dtype=x.dtype, device=x.device)
         if self.impl == "fused":
             self.ov.gemm_reducescatter_fused(x.contiguous(), weight, out, self.algo)

@@ -72,3 +72,33 @@ def test_fused_protocol_model_matches_sum():
         for r, o in enumerate(outs):
             got = layout.from_reordered(o, M // 2, N, BM // 2, BN, RA)
             assert torch.allclose(got, full[layout.owned_rows(M, BM, 2, r, strided)], atol=1e-5)
+
+
+def _decoder_layer_worker(rank, world):
+    """The TP decoder layer's data flow on CPU ranks: the `fused` token ownership (every 128-token
+    tile split across the ranks, activations gathered tile-interleaved and never re-ordered,
+    SwiGLU written into token order through a strided view) against the `nccl` one (contiguous
+    token shards).  Same weights, fp32."""
+    from flashoverlap_b200.models import DecoderConfig, TPDecoderLayer
+    cfg = DecoderConfig(hidden=256, ffn=512, n_heads=4, n_kv_heads=2, head_dim=32)
+    batch, seq = 2, 128
+    T = batch * seq
+    g = torch.Generator().manual_seed(11)
+    x_full = torch.randn(T, cfg.hidden, generator=g)
+    outs = {}
+    with torch.no_grad():
+        for mode in ("nccl", "fused"):
+            layer = TPDecoderLayer(cfg, rank, world, batch, seq, impl=mode, dtype=torch.float32, device="cpu", seed=3)
+            rows = layer.shard_rows()
+            full = torch.zeros(T, cfg.hidden)
+            full[rows] = layer(x_full[rows])
+            dist.all_reduce(full)
+            outs[mode] = full
+    return {"err": (outs["nccl"] - outs["fused"]).abs().max().item(), "scale": outs["nccl"].abs().max().item(),
+            "interleaved": bool((rows[:64] != torch.arange(rank * (T // world), rank * (T // world) + 64)).any()) if rank else True}
+
+
+def test_decoder_layer_fused_token_ownership_matches_contiguous_shards():
+    for r in run_ranks(_decoder_layer_worker, 2, "gloo", timeout_s=120):
+        assert r["interleaved"]
+        assert r["err"] <= 1e-4 * max(1.0, r["scale"]), r
